@@ -1,0 +1,85 @@
+// Shared helpers of the kernel libraries: dtype codes, loads that widen to float,
+// block reductions in a fixed order, and the layout of the paged cache.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+// dtype codes of the C ABI
+#define DT_F32 0
+#define DT_BF16 1
+
+// Step metadata: one int32 buffer per step, uploaded in one copy.  The first
+// words are a header; kernels read sizes that may differ from the launch's
+// (padded) sizes from there, so a captured graph serves any smaller batch.
+#define META_NUM_TOKENS 0
+#define META_NUM_ENTRIES 1
+#define META_NUM_ROWS 2
+#define META_BT_STRIDE 4   // + group (up to 8 groups)
+#define META_BT_OFFSET 12  // + group: where the group's block tables start, in ints
+#define META_HEADER_INTS 20
+
+// Status words (a device int32 array the host reads after a step); non-zero = fault.
+#define STATUS_BAD_TOKEN 0
+#define STATUS_BAD_PAGE 1
+#define STATUS_WORDS 4
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// Paged cache of one layer: [num_pages, 2 (K, V), num_kv_heads, page_size, head_dim].
+// The (page, K|V, head) block of page_size*head_dim elements is contiguous.
+struct CacheLayout {
+    int num_kv_heads, page_size, head_dim;
+    __host__ __device__ size_t page_elems() const { return (size_t)2 * num_kv_heads * page_size * head_dim; }
+    __host__ __device__ size_t offset(int page, int kv, int head, int slot) const {
+        return (((size_t)page * 2 + kv) * num_kv_heads + head) * (size_t)page_size * head_dim + (size_t)slot * head_dim;
+    }
+};
+
+// Sum over a block in a fixed order (warp shuffles, then warp 0 over the warp sums):
+// the result depends on the values only, not on timing.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// `scratch` holds 33 floats in shared memory.  All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < nwarps ? scratch[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+#define LAUNCH_RETURN() return (int)cudaGetLastError()

@@ -1,0 +1,366 @@
+// Core kernels, for float32 and bfloat16 storage alike; all arithmetic is float32.
+//
+// These are the plain kernels of the engine: the whole float32 path runs on them,
+// and the bfloat16 path uses them wherever no faster kernel exists for a size.
+// Every reduction runs in an order that depends only on the element it belongs to
+// (never on the batch, the portioning of a prompt, or the pages used), so float32
+// logits are bit-identical however the work is cut.
+//
+// What they stand for in the reference: candle's embedding, RmsNorm, rope, silu and
+// mul (models/src/llama.rs:470, 402-408, 218-251, 362-366), reshape_and_cache_flash
+// (csrc/kernels/cache_manager.cu:139-170) and the paged attention kernels
+// (csrc/kernels/flash_fwd_kernel.h).
+#include "common.cuh"
+
+// ----------------------------------------------------------------------------- embedding
+// resid[t, :] = table[tokens[t], :], widened to float32 (the residual stream is float32).
+template <typename T>
+__global__ void embed_rows_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                                  float* __restrict__ resid, const int* __restrict__ meta, int H, int V,
+                                  int* __restrict__ status) {
+    int t = blockIdx.x;
+    if (t >= meta[META_NUM_TOKENS]) return;
+    int tok = tokens[t];
+    bool bad = tok < 0 || tok >= V;
+    if (bad && threadIdx.x == 0) atomicExch(&status[STATUS_BAD_TOKEN], 1 + t);
+    const T* row = table + (size_t)(bad ? 0 : tok) * H;
+    float* out = resid + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = bad ? 0.f : to_float(row[i]);
+}
+
+extern "C" int embed_rows(const int* tokens, const void* table, int table_dtype, float* resid, const int* meta,
+                          int T, int H, int V, int* status, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == DT_F32)
+        embed_rows_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, resid, meta, H, V, status);
+    else
+        embed_rows_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, resid, meta, H, V, status);
+    LAUNCH_RETURN();
+}
+
+// ----------------------------------------------------------------------------- RMSNorm
+// resid[t] += delta[t] (if delta), out[t] = resid[t] * rsqrt(mean(resid[t]^2) + eps) * w.
+// With `rows`: works on rows[r] of resid/delta, writes out[r], leaves resid untouched.
+template <typename TD, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
+                                   const int* __restrict__ rows, const float* __restrict__ w, float eps,
+                                   TO* __restrict__ out, const int* __restrict__ meta, int H) {
+    __shared__ float red[33];
+    int r = blockIdx.x;
+    int limit = rows ? meta[META_NUM_ROWS] : meta[META_NUM_TOKENS];
+    if (r >= limit) return;
+    size_t src = rows ? (size_t)rows[r] : (size_t)r;
+    float* x = resid + src * H;
+    const TD* dl = delta ? delta + src * H : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = x[i];
+        if (dl) {
+            v += to_float(dl[i]);
+            if (!rows) x[i] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    float inv = rsqrtf(ss / (float)H + eps);
+    TO* o = out + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = x[i];
+        if (dl && rows) v += to_float(dl[i]);
+        o[i] = from_float<TO>(v * inv * w[i]);
+    }
+}
+
+extern "C" int add_rmsnorm(float* resid, const void* delta, int delta_dtype, const int* rows, const float* w,
+                           float eps, void* out, int out_dtype, const int* meta, int n, int H,
+                           cudaStream_t stream) {
+    if (n <= 0) return 0;
+    int threads = H >= 1024 ? 256 : 128;
+#define NORM_CASE(TD, TO) \
+    add_rmsnorm_kernel<TD, TO><<<n, threads, 0, stream>>>(resid, (const TD*)delta, rows, w, eps, (TO*)out, meta, H)
+    if (delta_dtype == DT_F32 && out_dtype == DT_F32) NORM_CASE(float, float);
+    else if (delta_dtype == DT_BF16 && out_dtype == DT_BF16) NORM_CASE(__nv_bfloat16, __nv_bfloat16);
+    else if (delta_dtype == DT_F32 && out_dtype == DT_BF16) NORM_CASE(float, __nv_bfloat16);
+    else NORM_CASE(__nv_bfloat16, float);
+#undef NORM_CASE
+    LAUNCH_RETURN();
+}
+
+// ----------------------------------------------------------------------------- float32 GEMM
+// y[M, N] = x[M, K] * w[N, K]^T, plain FFMA.  Each output element is one accumulator
+// running over k = 0..K-1 in order, so its value does not depend on M or on the tile
+// it falls in.  No tensor cores, no TF32.
+#define GB 64
+#define GK 16
+__global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__ x, const float* __restrict__ w,
+                                                       float* __restrict__ y, int M, int N, int K) {
+    __shared__ float xs[GK][GB + 4];
+    __shared__ float ws[GK][GB + 4];
+    int m0 = blockIdx.y * GB, n0 = blockIdx.x * GB;
+    int tx = threadIdx.x % 16, ty = threadIdx.x / 16;  // 16 x 16 threads, 4 x 4 outputs each
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += GK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            int idx = threadIdx.x + i * 256;  // 0..1023 over a 64 x 16 tile
+            int r = idx / GK, c = idx % GK;
+            int gm = m0 + r, gn = n0 + r, gk = k0 + c;
+            xs[c][r] = (gm < M && gk < K) ? x[(size_t)gm * K + gk] : 0.f;
+            ws[c][r] = (gn < N && gk < K) ? w[(size_t)gn * K + gk] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GK; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = xs[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = ws[kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        int gm = m0 + ty * 4 + i;
+        if (gm >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            int gn = n0 + tx * 4 + j;
+            if (gn < N) y[(size_t)gm * N + gn] = acc[i][j];
+        }
+    }
+}
+
+extern "C" int gemm_f32(const float* x, const float* w, float* y, int M, int N, int K, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    dim3 grid((N + GB - 1) / GB, (M + GB - 1) / GB);
+    gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, w, y, M, N, K);
+    LAUNCH_RETURN();
+}
+
+// ----------------------------------------------------------------------------- rotation + cache write
+// One row of the fused projection per token: [q (nq heads) | k (nkv heads) | v (nkv heads)].
+// Rotates q in place and writes rotated k and plain v to the token's slot of its page.
+// angle = position * inv_freq[i] in float32; pairs are (x[i], x[i + rot/2]) within the
+// first `rot` dims of a head (models/src/llama.rs:189-198, :250).  With store_kv = 0
+// (a layer that reads another layer's cache) only q is rotated.
+template <typename T>
+__global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                     const int* __restrict__ token_entry, const int* __restrict__ meta, int group,
+                                     const float* __restrict__ inv_freq, T* __restrict__ cache, CacheLayout L,
+                                     int nq, int rot, int store_kv, int num_pages, int* __restrict__ status) {
+    int t = blockIdx.x;
+    if (t >= meta[META_NUM_TOKENS]) return;
+    const int d = L.head_dim, nkv = L.num_kv_heads, half = rot / 2;
+    const int pos = positions[t];
+    T* row = qkv + (size_t)t * (nq + 2 * nkv) * d;
+    int page = 0, slot = 0;
+    if (store_kv) {
+        const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)token_entry[t] * meta[META_BT_STRIDE + group];
+        page = bt[pos / L.page_size];
+        slot = pos % L.page_size;
+        if (page <= 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + t);
+            store_kv = 0;
+        }
+    }
+    // rotated pairs of q and k heads
+    int pairs = (nq + nkv) * half;
+    for (int idx = threadIdx.x; idx < pairs; idx += blockDim.x) {
+        int h = idx / half, i = idx % half;
+        float ang = (float)pos * inv_freq[i];
+        float s, c;
+        sincosf(ang, &s, &c);
+        T* x = row + (size_t)h * d;
+        float a = to_float(x[i]), b = to_float(x[i + half]);
+        T ra = from_float<T>(a * c - b * s), rb = from_float<T>(a * s + b * c);
+        if (h < nq) {
+            x[i] = ra;
+            x[i + half] = rb;
+        } else if (store_kv) {
+            T* dst = cache + L.offset(page, 0, h - nq, slot);
+            dst[i] = ra;
+            dst[i + half] = rb;
+        }
+    }
+    if (!store_kv) return;
+    // dims of k beyond the rotated part, and all of v
+    int tail = d - rot;
+    for (int idx = threadIdx.x; idx < nkv * tail; idx += blockDim.x) {
+        int h = idx / tail, i = rot + idx % tail;
+        cache[L.offset(page, 0, h, slot) + i] = row[(size_t)(nq + h) * d + i];
+    }
+    for (int idx = threadIdx.x; idx < nkv * d; idx += blockDim.x) {
+        int h = idx / d, i = idx % d;
+        cache[L.offset(page, 1, h, slot) + i] = row[(size_t)(nq + nkv + h) * d + i];
+    }
+}
+
+extern "C" int rope_kv_store(void* qkv, int dtype, const int* positions, const int* token_entry, const int* meta,
+                             int group, const float* inv_freq, void* cache, int num_pages, int T, int nq, int nkv,
+                             int d, int rot, int page_size, int store_kv, int* status, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    CacheLayout L{nkv, page_size, d};
+    int threads = 128;
+    if (dtype == DT_F32)
+        rope_kv_store_kernel<float><<<T, threads, 0, stream>>>((float*)qkv, positions, token_entry, meta, group, inv_freq,
+                                                                (float*)cache, L, nq, rot, store_kv, num_pages, status);
+    else
+        rope_kv_store_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((__nv_bfloat16*)qkv, positions, token_entry, meta,
+                                                                        group, inv_freq, (__nv_bfloat16*)cache, L, nq,
+                                                                        rot, store_kv, num_pages, status);
+    LAUNCH_RETURN();
+}
+
+// ----------------------------------------------------------------------------- attention over the cache
+// One block per (token, query head).  The query at position p reads the keys at
+// positions kstart..p of its request through the block table (kstart = 0, or
+// p - window + 1 for a windowed layer), 64 at a time in position order, with a
+// running maximum and sum (softmax in float32).  The order of every sum depends on
+// p and the window only, so the result is the same whether the token came alone,
+// in a portion of a prompt, or beside other requests.
+#define ATTN_KT 64
+#define ATTN_THREADS 128
+template <typename T>
+__global__ void __launch_bounds__(ATTN_THREADS)
+attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ cache, CacheLayout L,
+                    const int* __restrict__ meta, int group, const int* __restrict__ token_entry,
+                    const int* __restrict__ positions, T* __restrict__ out, int nq, int window, float scale,
+                    int num_pages, int* __restrict__ status) {
+    int t = blockIdx.x, h = blockIdx.y;
+    if (t >= meta[META_NUM_TOKENS]) return;
+    const int d = L.head_dim, ps = L.page_size, tid = threadIdx.x;
+    const int p = positions[t];
+    const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)token_entry[t] * meta[META_BT_STRIDE + group];
+    const int kvh = h / (nq / L.num_kv_heads);
+    extern __shared__ float sm[];
+    float* qs = sm;                // d
+    float* prob = qs + d;          // ATTN_KT
+    float* red = prob + ATTN_KT;   // 40
+    float* tile = red + 40;        // ATTN_KT * (d + 1)
+    const int ld = d + 1;
+    const T* qrow = q + (size_t)t * q_stride + (size_t)h * d;
+    for (int i = tid; i < d; i += ATTN_THREADS) qs[i] = to_float(qrow[i]);
+    float m = -INFINITY, l = 0.f;
+    float acc[2] = {0.f, 0.f};  // head sizes up to 2 * ATTN_THREADS
+    const int kstart = window > 0 ? max(0, p - window + 1) : 0;
+    for (int k0 = kstart; k0 <= p; k0 += ATTN_KT) {
+        const int n = min(ATTN_KT, p - k0 + 1);
+        __syncthreads();  // the previous tile's values are no longer read
+        for (int idx = tid; idx < n * d; idx += ATTN_THREADS) {
+            int j = idx / d, i = idx % d, pos = k0 + j;
+            int page = bt[pos / ps];
+            if (page <= 0 || page >= num_pages) {
+                atomicExch(&status[STATUS_BAD_PAGE], 1 + t);
+                tile[j * ld + i] = 0.f;
+            } else {
+                tile[j * ld + i] = to_float(cache[L.offset(page, 0, kvh, pos % ps) + i]);
+            }
+        }
+        __syncthreads();
+        float s = -INFINITY;
+        if (tid < n) {
+            float dot = 0.f;
+            for (int i = 0; i < d; ++i) dot = fmaf(qs[i], tile[tid * ld + i], dot);
+            s = dot * scale;
+        }
+        float m_new = fmaxf(m, block_max(s, red));
+        float pj = tid < n ? expf(s - m_new) : 0.f;
+        if (tid < ATTN_KT) prob[tid] = pj;
+        float tsum = block_sum(pj, red);  // its barriers also order the key reads before the value writes
+        float corr = expf(m - m_new);
+        l = l * corr + tsum;
+        m = m_new;
+        for (int idx = tid; idx < n * d; idx += ATTN_THREADS) {
+            int j = idx / d, i = idx % d, pos = k0 + j;
+            int page = bt[pos / ps];
+            bool ok = page > 0 && page < num_pages;
+            tile[j * ld + i] = ok ? to_float(cache[L.offset(page, 1, kvh, pos % ps) + i]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int a = 0; a < 2; ++a) {
+            int i = tid + a * ATTN_THREADS;
+            if (i < d) {
+                float o = acc[a] * corr;
+                for (int j = 0; j < n; ++j) o = fmaf(prob[j], tile[j * ld + i], o);
+                acc[a] = o;
+            }
+        }
+    }
+    T* orow = out + ((size_t)t * nq + h) * d;
+    float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+    for (int a = 0; a < 2; ++a) {
+        int i = tid + a * ATTN_THREADS;
+        if (i < d) orow[i] = from_float<T>(acc[a] * inv);
+    }
+}
+
+extern "C" int attn_generic(const void* q, int q_stride, const void* cache, int dtype, const int* meta, int group,
+                            const int* token_entry, const int* positions, void* out, int T, int nq, int nkv, int d,
+                            int page_size, int num_pages, int window, float scale, int* status,
+                            cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (d > 2 * ATTN_THREADS) return (int)cudaErrorInvalidValue;
+    CacheLayout L{nkv, page_size, d};
+    size_t smem = (size_t)(d + ATTN_KT + 40 + ATTN_KT * (d + 1)) * sizeof(float);
+    dim3 grid(T, nq);
+    cudaError_t e;
+    if (dtype == DT_F32) {
+        e = cudaFuncSetAttribute(attn_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attn_generic_kernel<float><<<grid, ATTN_THREADS, smem, stream>>>(
+            (const float*)q, q_stride, (const float*)cache, L, meta, group, token_entry, positions, (float*)out, nq,
+            window, scale, num_pages, status);
+    } else {
+        e = cudaFuncSetAttribute(attn_generic_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attn_generic_kernel<__nv_bfloat16><<<grid, ATTN_THREADS, smem, stream>>>(
+            (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, L, meta, group, token_entry, positions,
+            (__nv_bfloat16*)out, nq, window, scale, num_pages, status);
+    }
+    LAUNCH_RETURN();
+}
+
+// ----------------------------------------------------------------------------- SwiGLU gate
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(z) = z / (1 + exp(-z))  (models/src/llama.rs:364).
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, const int* __restrict__ meta, int I) {
+    int t = blockIdx.y;
+    if (t >= meta[META_NUM_TOKENS]) return;
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= I) return;
+    float g = to_float(gu[(size_t)t * 2 * I + i]), u = to_float(gu[(size_t)t * 2 * I + I + i]);
+    out[(size_t)t * I + i] = from_float<T>(g / (1.f + expf(-g)) * u);
+}
+
+extern "C" int silu_mul(const void* gu, void* out, int dtype, const int* meta, int T, int I, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    dim3 grid((I + 255) / 256, T);
+    if (dtype == DT_F32) silu_mul_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, meta, I);
+    else silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, meta, I);
+    LAUNCH_RETURN();
+}
+
+// ----------------------------------------------------------------------------- casts
+template <typename TI, typename TO>
+__global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = from_float<TO>(to_float(in[i]));
+}
+extern "C" int cast_f32_bf16(const float* in, void* out, size_t n, cudaStream_t stream) {
+    if (!n) return 0;
+    cast_kernel<float, __nv_bfloat16><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(in, (__nv_bfloat16*)out, n);
+    LAUNCH_RETURN();
+}
+extern "C" int cast_bf16_f32(const void* in, float* out, size_t n, cudaStream_t stream) {
+    if (!n) return 0;
+    cast_kernel<__nv_bfloat16, float><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)in, out, n);
+    LAUNCH_RETURN();
+}

@@ -1,0 +1,3 @@
+from .safetensors_io import SafetensorsError, SafetensorsFile, open_model_files, write_safetensors
+from .loader import TensorDecl, WeightError, load_tensors
+from .random_init import random_tensors, write_random_model
