@@ -10,3 +10,4 @@ replay), ``sampling``, ``csrc`` (CUDA kernels and the native host library).
 __version__ = "0.1.0"
 
 from .config import ConfigError, EngineConfig, LlamaConfig  # noqa: F401
+from . import models  # noqa: F401,E402  (registers the architectures)

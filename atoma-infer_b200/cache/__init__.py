@@ -1,3 +1,3 @@
-from .manager import (
-    FULL_KEYS, WINDOW_KEYS, CacheError, CacheGroup, CacheManager, CacheNeed, OutOfPages,
-)
+from .spec import FULL_KEYS, WINDOW_KEYS, CacheGroup, CacheNeed, LayerCache
+from .manager import CacheError, CacheManager, OutOfPages
+from .kv_cache import KVCache, page_bytes, pages_for_memory

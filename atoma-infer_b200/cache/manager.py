@@ -13,8 +13,7 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
 from ..csrc.build import host_library
-
-FULL_KEYS, WINDOW_KEYS = 0, 1
+from .spec import FULL_KEYS, WINDOW_KEYS, CacheGroup, CacheNeed
 
 _ERRORS = {
     -1: "out of pages", -2: "no free state slot", -3: "unknown request (or freed twice)",
@@ -31,28 +30,6 @@ class CacheError(RuntimeError):
 
 class OutOfPages(CacheError):
     pass
-
-
-@dataclass(frozen=True)
-class CacheNeed:
-    """What one mixer keeps per cached token: keys and values of ``num_kv_heads`` heads of
-    ``head_dim``; ``window`` = how many keys a query looks back over (itself included),
-    None for all of them."""
-
-    num_kv_heads: int
-    head_dim: int
-    window: Optional[int] = None
-
-    @property
-    def kind(self) -> int:
-        return FULL_KEYS if self.window is None else WINDOW_KEYS
-
-
-@dataclass
-class CacheGroup:
-    need: CacheNeed
-    layers: List[int] = field(default_factory=list)  # model layer indices that own a cache here
-    num_pages: int = 0  # pool size, page 0 (never handed out) included
 
 
 def _bind(lib):

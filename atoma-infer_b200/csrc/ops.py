@@ -1,0 +1,140 @@
+"""The kernels as Python calls on torch tensors.
+
+Every function launches hand-written CUDA from the libraries under ``kernels/``
+on torch's current stream; tensors are only memory here.  There is no CPU path:
+without a CUDA device the constructor raises.  Matrix products of the bfloat16
+path with many rows go to cuBLAS through ``torch.matmul``, as the reference sends
+its linears to cuBLAS through candle (models/src/llama.rs:269-271).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build
+
+DT_F32, DT_BF16 = 0, 1
+META_HEADER_INTS = 20
+META_NUM_TOKENS, META_NUM_ENTRIES, META_NUM_ROWS, META_BT_STRIDE, META_BT_OFFSET = 0, 1, 2, 4, 12
+MAX_GROUPS = 8
+STATUS_WORDS = 4
+SKINNY_MAX_ROWS = 16  # bfloat16 linears with at most this many rows stream the weights
+
+CORE_SOURCES = ["kernels/core.cu", "kernels/linear_bf16.cu", "kernels/sampling.cu"]
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _code(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return DT_F32
+    if t.dtype == torch.bfloat16:
+        return DT_BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+class CudaOps:
+    """Loads (building at first use) the kernel library and exposes its entry points."""
+
+    def __init__(self, device: torch.device):
+        if not torch.cuda.is_available():
+            raise KernelError("this engine runs on a CUDA device only; none is available")
+        self.device = torch.device(device)
+        self.lib = build.load_library("core", CORE_SOURCES, cuda=True)
+        self.status = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=self.device)
+        self.launches = 0  # own kernel launches, counted for the benchmark record
+
+    # ------------------------------------------------------------------ helpers
+    def _stream(self):
+        return ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def _check(self, err: int, what: str):
+        self.launches += 1
+        if err:
+            raise KernelError(f"{what}: CUDA error {err}")
+
+    def check_status(self) -> None:
+        """Raises if a kernel of an earlier launch met a bad token id or page id (synchronises)."""
+        s = self.status.tolist()
+        if any(s):
+            self.status.zero_()
+            raise KernelError(
+                f"device status: token id out of range at token {s[0] - 1}" if s[0] else
+                f"device status: block table names no valid page for token {s[1] - 1}"
+            )
+
+    # ------------------------------------------------------------------ kernels
+    def embed(self, tokens, table, resid, meta, T: int):
+        H, V = table.shape[1], table.shape[0]
+        self._check(self.lib.embed_rows(_p(tokens), _p(table), _code(table), _p(resid), _p(meta), T, H, V,
+                                        _p(self.status), self._stream()), "embed_rows")
+
+    def add_rmsnorm(self, resid, delta, w, eps: float, out, meta, n: int, rows=None):
+        """resid += delta (if given); out = rmsnorm(resid) * w.  With ``rows`` the sum and the
+        norm are taken at those rows only and resid is left as it is."""
+        H = resid.shape[-1]
+        self._check(self.lib.add_rmsnorm(_p(resid), _p(delta), _code(delta) if delta is not None else _code(out),
+                                         _p(rows), _p(w), ctypes.c_float(eps), _p(out), _code(out), _p(meta), n, H,
+                                         self._stream()), "add_rmsnorm")
+
+    def linear(self, x, w, *, out_dtype=None, silu_mul: bool = False, meta=None, use_rows: bool = False):
+        """x [M, K] times w [N, K] transposed.  ``silu_mul``: w is [gate; up] stacked and the
+        result is silu(gate part) * (up part), of N/2 columns."""
+        M, K = x.shape
+        N = w.shape[0]
+        out_dtype = out_dtype or x.dtype
+        n_out = N // 2 if silu_mul else N
+        if x.dtype == torch.float32:
+            y = torch.empty((M, N), dtype=torch.float32, device=x.device)
+            self._check(self.lib.gemm_f32(_p(x), _p(w), _p(y), M, N, K, self._stream()), "gemm_f32")
+            if silu_mul:
+                out = torch.empty((M, n_out), dtype=torch.float32, device=x.device)
+                self.silu_mul(y, out, meta, M, n_out)
+                return out
+            return y
+        if M <= SKINNY_MAX_ROWS and K % 8 == 0:
+            y = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+            self._check(self.lib.linear_skinny(_p(x), _p(w), _p(y), _code(y), int(silu_mul), _p(meta), int(use_rows),
+                                               M, N, K, self._stream()), "linear_skinny")
+            return y
+        if out_dtype == torch.float32:
+            y = torch.mm(x, w.t(), out_dtype=torch.float32)
+        else:
+            y = torch.mm(x, w.t())
+        if silu_mul:
+            out = torch.empty((M, n_out), dtype=x.dtype, device=x.device)
+            self.silu_mul(y, out, meta, M, n_out)
+            return out
+        return y
+
+    def silu_mul(self, gu, out, meta, T: int, inter: int):
+        self._check(self.lib.silu_mul(_p(gu), _p(out), _code(gu), _p(meta), T, inter, self._stream()), "silu_mul")
+
+    def rope_kv_store(self, qkv, positions, token_entry, meta, group: int, inv_freq, cache_layer, num_pages: int,
+                      T: int, nq: int, nkv: int, d: int, rot: int, page_size: int, store_kv: bool):
+        self._check(self.lib.rope_kv_store(_p(qkv), _code(qkv), _p(positions), _p(token_entry), _p(meta), group,
+                                           _p(inv_freq), _p(cache_layer), num_pages, T, nq, nkv, d, rot, page_size,
+                                           int(store_kv), _p(self.status), self._stream()), "rope_kv_store")
+
+    def attention(self, q, q_stride: int, cache_layer, meta, group: int, token_entry, positions, out, T: int, nq: int,
+                  nkv: int, d: int, page_size: int, num_pages: int, window: int, scale: float):
+        self._check(self.lib.attn_generic(_p(q), q_stride, _p(cache_layer), _code(q), _p(meta), group, _p(token_entry),
+                                          _p(positions), _p(out), T, nq, nkv, d, page_size, num_pages, window,
+                                          ctypes.c_float(scale), _p(self.status), self._stream()), "attn_generic")
+
+    def sample(self, logits, temperature, top_k, top_p, seed, step, out, num_rows=None):
+        R, V = logits.shape
+        self._check(self.lib.sample_rows(_p(logits), R, V, _p(temperature), _p(top_k), _p(top_p), _p(seed), _p(step),
+                                         _p(out), _p(num_rows), self._stream()), "sample_rows")
+
+    def repeat_penalty(self, row, penalty: float, context):
+        self._check(self.lib.repeat_penalty(_p(row), row.numel(), ctypes.c_float(penalty), _p(context),
+                                            context.numel(), self._stream()), "repeat_penalty")

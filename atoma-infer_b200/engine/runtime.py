@@ -1,0 +1,74 @@
+"""Putting a model on the device: configuration, weights, cache, step function.
+
+Start-up order as in the reference (backends/vllm/src/llm_service.rs:102-260): read
+the configuration, load the weights, then size the cache from the memory that is
+left (backends/vllm/src/config.rs:626-641) unless a page count is given, then build
+the worker's cache and the block manager over the same geometry.
+"""
+from __future__ import annotations
+
+import sys
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..cache.kv_cache import KVCache, pages_for_memory
+from ..cache.manager import CacheManager
+from ..config.engine_config import canonical_dtype
+from ..config.registry import architecture_of
+from ..csrc.ops import CudaOps
+from ..parts.base import Runtime
+from ..parts.model import DecoderModel
+from ..weights.loader import load_tensors
+from .step import StepFunction
+
+_TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+@dataclass
+class LoadedModel:
+    config: object
+    model: DecoderModel
+    rt: Runtime
+    manager: CacheManager
+    cache: KVCache
+    step: StepFunction
+    page_size: int
+    num_pages: int  # usable pages per pool
+
+
+def make_runtime(dtype: str, device=None, ops=None) -> Runtime:
+    tdtype = _TORCH_DTYPES[canonical_dtype(dtype)]
+    device = torch.device(device if device is not None else "cuda:0")
+    if tdtype == torch.float32:
+        # the 32-bit path is true float32 wherever a library product is used
+        torch.backends.cuda.matmul.allow_tf32 = False
+        torch.backends.cudnn.allow_tf32 = False
+    return Runtime(device=device, dtype=tdtype, ops=ops if ops is not None else CudaOps(device))
+
+
+def load_model(model_dir: str, *, dtype: str = "bfloat16", device=None, page_size: int = 16,
+               num_pages: Optional[int] = None, max_seqs: int = 64, gpu_memory_utilization: float = 0.9,
+               poison_cache: bool = False, ops=None) -> LoadedModel:
+    """``num_pages``: usable pages per pool; None sizes the pools from free device memory."""
+    arch, config = architecture_of(model_dir)
+    spec = arch.build_spec(config)
+    model = DecoderModel(spec)
+    rt = make_runtime(dtype, device, ops)
+    tensors = load_tensors(model_dir, model.declare(), dtype=rt.dtype, device=rt.device, ignore=spec.ignored_tensors)
+    model.bind(tensors, rt)
+    del tensors
+    groups = model.groups
+    if num_pages is None:
+        free, total = torch.cuda.mem_get_info(rt.device)
+        budget = int(free - (1.0 - gpu_memory_utilization) * total)
+        num_pages = pages_for_memory(groups, page_size, rt.dtype, budget) - 1
+        if num_pages <= 0:
+            raise RuntimeError("no device memory is left for the cache after loading the weights")
+    for g in groups:
+        g.num_pages = num_pages + 1  # page 0 is never handed out
+    manager = CacheManager(page_size, groups, max_seqs)
+    cache = KVCache(model, groups, page_size, max_seqs, rt, poison=poison_cache)
+    step = StepFunction(model, cache, manager, rt)
+    return LoadedModel(config, model, rt, manager, cache, step, page_size, num_pages)

@@ -1,0 +1,167 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A step takes any mix of prompt portions and single decoded tokens, cut anywhere,
+runs only those tokens, from the cache that earlier steps left, and returns
+float32 logits at the wanted places only.  It claims the pages the tokens need,
+builds the step's metadata in one int32 buffer (one host-to-device copy; the
+reference uploads about ten small tensors, backends/vllm/src/worker.rs:411-434),
+runs the model's forward pass and advances the requests in the cache manager.
+
+The reference's counterpart is ModelWorker::execute_model with
+prepare_input_tensors (backends/vllm/src/worker.rs:111-191, 224-460); it returns
+the last row of every sequence (:166, 688-698) and cannot run a later portion of a
+prompt against its cached part (models/src/flash_attention.rs:384-410).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.kv_cache import KVCache
+from ..cache.manager import CacheManager
+from ..csrc.ops import (MAX_GROUPS, META_BT_OFFSET, META_BT_STRIDE, META_HEADER_INTS, META_NUM_ENTRIES,
+                        META_NUM_ROWS, META_NUM_TOKENS)
+from ..parts.base import EntryInfo, Runtime, StepContext
+
+
+@dataclass
+class StepEntry:
+    """A request's share of a step: its next tokens and the places (indices into these
+    tokens) whose logits are wanted."""
+
+    req: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+@dataclass
+class MetaLayout:
+    """Where each array lies in the metadata buffer, for given capacities."""
+
+    T: int
+    S: int
+    R: int
+    strides: Tuple[int, ...]  # block-table row length per group
+
+    def __post_init__(self):
+        o = META_HEADER_INTS
+        self.tokens = o; o += self.T
+        self.positions = o; o += self.T
+        self.token_entry = o; o += self.T
+        self.cu = o; o += self.S + 1
+        self.ctx = o; o += self.S
+        self.slots = o; o += self.S
+        self.rows = o; o += max(self.R, 1)
+        self.tables = []
+        for s in self.strides:
+            self.tables.append(o)
+            o += self.S * s
+        self.size = o
+
+
+class StepFunction:
+    def __init__(self, model, cache: KVCache, manager: CacheManager, rt: Runtime):
+        if len(manager.groups) > MAX_GROUPS:
+            raise ValueError(f"at most {MAX_GROUPS} cache groups are supported")
+        self.model, self.cache, self.manager, self.rt = model, cache, manager, rt
+        self.page_size = manager.page_size
+        self._pinned = torch.cuda.is_available()
+        self.steps = 0
+
+    # ------------------------------------------------------------------ metadata
+    def _host_buffer(self, n: int) -> torch.Tensor:
+        return torch.empty(n, dtype=torch.int32, pin_memory=self._pinned)
+
+    def prepare(self, entries: Sequence[StepEntry]):
+        """Claims pages, builds the metadata on the host.  Returns (host buffer, layout, infos, R)."""
+        mgr, ps = self.manager, self.page_size
+        infos: List[EntryInfo] = []
+        seen = set()
+        start = 0
+        for e in entries:
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.req} brings no tokens")
+            if e.req in seen:
+                raise ValueError(f"request {e.req} appears twice in one step")
+            seen.add(e.req)
+            is_new = not mgr.has_request(e.req)
+            slot = mgr.add_request(e.req) if is_new else mgr.state_slot(e.req)
+            ctx_len = mgr.num_tokens(e.req)
+            try:
+                mgr.reserve(e.req, ctx_len + n)
+            except Exception:
+                if is_new:
+                    mgr.free_request(e.req)
+                raise
+            for w in e.want:
+                if not (0 <= w < n):
+                    raise ValueError(f"request {e.req}: wanted place {w} is outside its {n} tokens")
+            infos.append(EntryInfo(e.req, start, n, ctx_len, slot, is_new))
+            start += n
+        T, S = start, len(infos)
+        R = sum(len(e.want) for e in entries)
+        strides = tuple(max((mgr.table_len(i.req, g) for i in infos), default=1) for g in range(len(mgr.groups)))
+        lay = MetaLayout(T, S, R, strides)
+        host = self._host_buffer(lay.size)
+        h = host.numpy()
+        h[:META_HEADER_INTS] = 0
+        h[META_NUM_TOKENS], h[META_NUM_ENTRIES], h[META_NUM_ROWS] = T, S, R
+        rows = []
+        for k, (e, i) in enumerate(zip(entries, infos)):
+            a, b = i.start, i.start + i.num_tokens
+            h[lay.tokens + a:lay.tokens + b] = np.asarray(e.tokens, dtype=np.int64)
+            h[lay.positions + a:lay.positions + b] = np.arange(i.context_len, i.context_len + i.num_tokens)
+            h[lay.token_entry + a:lay.token_entry + b] = k
+            h[lay.cu + k] = a
+            h[lay.ctx + k] = i.context_len
+            h[lay.slots + k] = i.state_slot
+            rows += [a + w for w in e.want]
+        h[lay.cu + S] = T
+        if rows:
+            h[lay.rows:lay.rows + R] = rows
+        base = h.ctypes.data
+        for g, (off, stride) in enumerate(zip(lay.tables, strides)):
+            h[META_BT_STRIDE + g], h[META_BT_OFFSET + g] = stride, off
+            h[off:off + S * stride] = -1
+            for k, i in enumerate(infos):
+                mgr.table_into(i.req, g, base + 4 * (off + k * stride), stride)
+        return host, lay, infos, R
+
+    def context(self, dev: torch.Tensor, lay: MetaLayout, infos: List[EntryInfo]) -> StepContext:
+        v = lambda o, n: dev[o:o + n]  # noqa: E731
+        return StepContext(
+            rt=self.rt, T=lay.T, S=lay.S, meta=dev,
+            tokens=v(lay.tokens, lay.T), positions=v(lay.positions, lay.T), token_entry=v(lay.token_entry, lay.T),
+            cu_tokens=v(lay.cu, lay.S + 1), context_lens=v(lay.ctx, lay.S), state_slots=v(lay.slots, lay.S),
+            entries=infos,
+            max_tokens_per_entry=max((i.num_tokens for i in infos), default=0),
+            max_context=max((i.context_len + i.num_tokens for i in infos), default=0),
+            decode_only=all(i.num_tokens == 1 for i in infos),
+            page_size=self.page_size,
+        )
+
+    # ------------------------------------------------------------------ the step
+    def run(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs the step; returns float32 logits [wanted places, vocab] on the device, in the
+        order of the entries and of their ``want`` lists."""
+        if not entries:
+            return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
+        host, lay, infos, R = self.prepare(entries)
+        dev = host.to(self.rt.device, non_blocking=True)
+        for i in infos:
+            if i.is_new:
+                self.cache.reset_state(i.state_slot)
+        ctx = self.context(dev, lay, infos)
+        logits = self.model.forward(ctx, self.cache, dev[lay.rows:lay.rows + max(R, 1)], R)
+        for i in infos:
+            self.manager.advance(i.req, i.num_tokens)
+        self.steps += 1
+        return logits
+
+    def finish(self, req: int) -> None:
+        """The request ends: its pages and its state slot go back to the pools."""
+        self.manager.free_request(req)

@@ -1,0 +1,134 @@
+"""A model as data: layers chosen part by part, and the order in which they run.
+
+``ModelSpec`` is what an architecture's builder returns from its configuration:
+per layer the kinds and parameters of block, mixer, feed-forward and norm, and a
+``schedule`` — the list of layer runs.  A run names the layer to execute and the
+layer whose cache it uses, so a layer may run twice or read another layer's keys
+and values.  ``DecoderModel`` turns the spec into bound parts and runs a step:
+embedding, the scheduled blocks, the final norm at the wanted rows, the output head
+(models/src/llama.rs:456-478 has this sequence fixed for one model).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.spec import CacheGroup, CacheNeed
+from ..config.registry import part_class
+from ..weights.loader import TensorDecl
+from .base import LayerCache, Runtime, StepContext
+
+# the registrations of the built-in parts
+from . import attention, block, feed_forward, norm, position  # noqa: F401
+
+
+@dataclass
+class LayerSpec:
+    prefix: str              # checkpoint prefix of the layer, e.g. "model.layers.3"
+    block: Dict[str, Any]    # {"kind": "prenorm", "norm": {...}, "mixer": {...}, "feed_forward": {...}}
+
+
+@dataclass
+class LayerRun:
+    layer: int                       # index into ModelSpec.layers
+    cache_of: Optional[int] = None   # layer whose cache this run uses (None: its own)
+
+
+@dataclass
+class ModelSpec:
+    hidden_size: int
+    vocab_size: int
+    layers: List[LayerSpec]
+    final_norm: Dict[str, Any]
+    embedding_tensor: str = "model.embed_tokens.weight"
+    final_norm_prefix: str = "model.norm"
+    head_tensor: Optional[str] = "lm_head.weight"   # None: the embedding matrix is the head
+    schedule: Optional[List[LayerRun]] = None       # None: every layer once, in order
+    ignored_tensors: Tuple[str, ...] = ()           # globs a checkpoint may carry unused
+    max_position: int = 0
+    eos_token_ids: Tuple[int, ...] = ()
+
+    def runs(self) -> List[LayerRun]:
+        return self.schedule if self.schedule is not None else [LayerRun(i) for i in range(len(self.layers))]
+
+
+def _build_layers(spec: ModelSpec):
+    return [part_class("block", ls.block["kind"])(ls.block, ls.prefix) for ls in spec.layers]
+
+
+def declared_tensors(spec: ModelSpec) -> List[TensorDecl]:
+    """Every checkpoint tensor the model needs, by name and shape."""
+    decls = [TensorDecl(spec.embedding_tensor, (spec.vocab_size, spec.hidden_size))]
+    for blk in _build_layers(spec):
+        decls += blk.declare()
+    decls += part_class("norm", spec.final_norm["kind"])(spec.final_norm, spec.final_norm_prefix).declare()
+    if spec.head_tensor:
+        decls.append(TensorDecl(spec.head_tensor, (spec.vocab_size, spec.hidden_size)))
+    return decls
+
+
+class DecoderModel:
+    """Bound parts of one model plus the plan of its cache."""
+
+    def __init__(self, spec: ModelSpec):
+        self.spec = spec
+        self.blocks = _build_layers(spec)
+        self.final_norm = part_class("norm", spec.final_norm["kind"])(spec.final_norm, spec.final_norm_prefix)
+        self.runs = spec.runs()
+        for r in self.runs:
+            if not (0 <= r.layer < len(self.blocks)):
+                raise ValueError(f"schedule names layer {r.layer}, the model has {len(self.blocks)}")
+            owner = r.layer if r.cache_of is None else r.cache_of
+            if not (0 <= owner < len(self.blocks)):
+                raise ValueError(f"schedule lets layer {r.layer} read the cache of layer {owner}, which does not exist")
+            a, b = self.blocks[r.layer].mixer.cache_need(), self.blocks[owner].mixer.cache_need()
+            if a != b:
+                raise ValueError(f"layer {r.layer} cannot read the cache of layer {owner}: {a} != {b}")
+        # Cache groups: layers that own a cache, put together by what they need.  A layer
+        # owns a cache if some run uses it as its cache layer.
+        owners = sorted({(r.layer if r.cache_of is None else r.cache_of) for r in self.runs})
+        self.groups: List[CacheGroup] = []
+        self.layer_group: Dict[int, Tuple[int, int]] = {}  # layer -> (group, index within the group)
+        for layer in owners:
+            need = self.blocks[layer].mixer.cache_need()
+            if need is None:
+                continue
+            for gi, g in enumerate(self.groups):
+                if g.need == need:
+                    break
+            else:
+                self.groups.append(CacheGroup(need))
+                gi = len(self.groups) - 1
+            self.layer_group[layer] = (gi, len(self.groups[gi].layers))
+            self.groups[gi].layers.append(layer)
+        self.state_bytes = [blk.mixer.state_bytes() for blk in self.blocks]
+
+    def declare(self) -> List[TensorDecl]:
+        return declared_tensors(self.spec)
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
+        self.rt = rt
+        self.embedding = tensors[self.spec.embedding_tensor]
+        self.head = tensors[self.spec.head_tensor] if self.spec.head_tensor else self.embedding
+        for blk in self.blocks:
+            blk.bind(tensors, rt)
+        self.final_norm.bind(tensors, rt)
+
+    # ------------------------------------------------------------------ the forward pass of one step
+    def forward(self, ctx: StepContext, cache, rows: torch.Tensor, num_rows: int) -> torch.Tensor:
+        """Runs the step's tokens through the model; returns float32 logits [num_rows, vocab]
+        at the flat-batch rows listed in ``rows`` (a device int32 array)."""
+        ops = self.rt.ops
+        resid = torch.empty((ctx.T, self.spec.hidden_size), dtype=torch.float32, device=self.rt.device)
+        ops.embed(ctx.tokens, self.embedding, resid, ctx.meta, ctx.T)
+        delta = None
+        for run in self.runs:
+            owner = run.layer if run.cache_of is None else run.cache_of
+            delta = self.blocks[run.layer].forward(resid, delta, ctx, cache.layer_view(owner, writes=run.cache_of is None,
+                                                                                        state_layer=run.layer))
+        if num_rows == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
+        h = self.final_norm.forward(resid, delta, ctx, rows=rows, num_rows=num_rows)
+        return ops.linear(h, self.head, out_dtype=torch.float32, meta=ctx.meta, use_rows=True)

@@ -47,7 +47,7 @@ class SafetensorsFile:
             raise SafetensorsError(f"{path}: header is not JSON ({e})") from None
         self.metadata = header.pop("__metadata__", {})
         self._base = 8 + n
-        self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
+        self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_COPY)
         self.entries: Dict[str, Tuple[torch.dtype, Tuple[int, ...], int, int]] = {}
         for name, e in header.items():
             if e["dtype"] not in _DTYPES:

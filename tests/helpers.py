@@ -1,0 +1,174 @@
+"""Shared test material: two tiny configurations that differ in every size and option,
+model folders with random weights, trace builders for the replay program, comparison."""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+from typing import Dict, List, Sequence
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import atoma_infer_b200  # noqa: E402,F401
+from atoma_infer_b200.weights import write_random_model  # noqa: E402
+from atoma_infer_b200.weights.safetensors_io import SafetensorsFile  # noqa: E402
+
+# A: grouped-query 2:1, head 16, tied head, no frequency scaling, page 4
+CONFIG_A = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 64, "intermediate_size": 176, "vocab_size": 256,
+    "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "rms_norm_eps": 1e-5,
+    "rope_theta": 10000.0, "max_position_embeddings": 1024, "tie_word_embeddings": True, "eos_token_id": 255,
+}
+# B: one key/value head for three query heads, head 64, untied head, llama3 scaling whose
+# original length (64) puts frequencies in all three bands, page 8, sizes that are no power of two
+CONFIG_B = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 192, "intermediate_size": 320, "vocab_size": 1000,
+    "num_hidden_layers": 3, "num_attention_heads": 3, "num_key_value_heads": 1, "rms_norm_eps": 1e-6,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 64, "rope_type": "llama3"},
+    "max_position_embeddings": 1024, "tie_word_embeddings": False, "eos_token_id": [998, 999],
+}
+TINY = {"A": (CONFIG_A, 4), "B": (CONFIG_B, 8)}  # name -> (config, page size)
+
+FP32_TOL = 2e-5   # times the largest |logit| of the sequence
+BF16_TOL = 3e-2
+
+
+def make_model(path: str, config: dict, seed: int = 0, **kw) -> str:
+    """Random weights large enough that attention and norms matter (std 0.05, norm weights 1 +- 0.1)."""
+    kw.setdefault("std", 0.05)
+    kw.setdefault("norm_jitter", 0.1)
+    return write_random_model(path, config, seed, **kw)
+
+
+def read_weights(model_dir: str) -> Dict[str, torch.Tensor]:
+    f = SafetensorsFile(os.path.join(model_dir, "model.safetensors"))
+    return {n: f.tensor(n).to(torch.float32) for n in f.names()}
+
+
+def random_tokens(vocab: int, lengths: Sequence[int], seed: int) -> Dict[str, List[int]]:
+    g = torch.Generator().manual_seed(seed)
+    return {f"r{i}": torch.randint(0, vocab, (n,), generator=g).tolist() for i, n in enumerate(lengths)}
+
+
+# ------------------------------------------------------------------ traces
+def trace_whole(seqs, tag="w"):
+    return [{"entries": [{"id": f"{tag}{k}", "tokens": v, "want": list(range(len(v)))}], "end": [f"{tag}{k}"]}
+            for k, v in seqs.items()]
+
+
+def trace_tail(seqs, tail=32, tag="t"):
+    """Most of a request in one step, its last ``tail`` tokens one by one."""
+    steps = []
+    for k, v in seqs.items():
+        head = max(len(v) - tail, 0)
+        if head:
+            steps.append({"entries": [{"id": f"{tag}{k}", "tokens": v[:head], "want": list(range(head))}], "end": []})
+        for i in range(head, len(v)):
+            steps.append({"entries": [{"id": f"{tag}{k}", "tokens": [v[i]], "want": [0]}],
+                          "end": [f"{tag}{k}"] if i == len(v) - 1 else []})
+    return steps
+
+
+def trace_chunks(seqs, sizes=(5, 2, 7, 3, 2, 11, 1, 4), tag="c"):
+    """Portions of changing size, down to two tokens (and one)."""
+    steps, si = [], 0
+    for k, v in seqs.items():
+        pos = 0
+        while pos < len(v):
+            n = min(sizes[si % len(sizes)], len(v) - pos)
+            si += 1
+            steps.append({"entries": [{"id": f"{tag}{k}", "tokens": v[pos:pos + n], "want": list(range(n))}],
+                          "end": [f"{tag}{k}"] if pos + n == len(v) else []})
+            pos += n
+    return steps
+
+
+def trace_mixed(seqs, max_live=4, sizes=(6, 2, 9, 3, 5), tag="m", seed=0):
+    """Up to ``max_live`` requests at a time; each either runs a portion of its prompt, a
+    single token (as a decode step would) or sits a step out; new requests take the
+    pages of ended ones."""
+    rng = np.random.RandomState(seed)
+    pending = list(seqs)
+    live, pos, steps, si = [], {k: 0 for k in seqs}, [], 0
+    single = {k: i % 2 == 1 for i, k in enumerate(seqs)}  # every other request: one token at a time after a start
+    while pending or live:
+        while pending and len(live) < max_live:
+            live.append(pending.pop(0))
+        entries, end = [], []
+        for k in list(live):
+            if len(live) > 1 and rng.rand() < 0.2:
+                continue  # left out of this step, goes on later
+            v = seqs[k]
+            if single[k] and pos[k] >= min(len(v) // 2, 8):
+                n = 1
+            else:
+                n = sizes[si % len(sizes)]
+                si += 1
+            n = min(n, len(v) - pos[k])
+            entries.append({"id": f"{tag}{k}", "tokens": v[pos[k]:pos[k] + n], "want": list(range(n))})
+            pos[k] += n
+            if pos[k] == len(v):
+                end.append(f"{tag}{k}")
+                live.remove(k)
+        if entries:
+            steps.append({"entries": entries, "end": end})
+    return steps
+
+
+def number(steps):
+    return [dict(s, step=i) for i, s in enumerate(steps)]
+
+
+def run_trace(model_dir: str, dtype: str, steps, out_dir: str, max_tokens: int, page_size: int, timeout=600):
+    """Runs bin/trace_run as a user would; returns the list of per-step arrays (None where nothing was wanted)."""
+    steps = number(steps)
+    text = "\n".join(json.dumps(s) for s in steps) + "\n"
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
+           "--out", out_dir, "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
+    p = subprocess.run(cmd, input=text, capture_output=True, text=True, timeout=timeout)
+    assert p.returncode == 0, f"trace_run failed ({p.returncode}):\n{p.stdout[-2000:]}\n{p.stderr[-4000:]}"
+    done = [l for l in p.stdout.splitlines() if l.startswith("done ")]
+    assert [int(l.split()[1]) for l in done] == [s["step"] for s in steps], "a 'done <step>' line is missing"
+    return steps, out_dir
+
+
+def compare_trace(steps, out_dir: str, vocab: int, ref_logits: Dict[str, torch.Tensor], strip=1):
+    """Largest |difference| / largest |logit| over every wanted place, and the first place
+    where it exceeds nothing (for messages).  Request ids carry a ``strip``-letter tag."""
+    pos: Dict[str, int] = {}
+    worst, where = 0.0, None
+    agree = total = 0
+    for s in steps:
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        if not wanted:
+            for e in s["entries"]:
+                pos[e["id"]] = pos.get(e["id"], 0) + len(e["tokens"])
+            continue
+        got = np.fromfile(os.path.join(out_dir, f"{s['step']}.f32"), dtype="<f4").reshape(-1, vocab)
+        assert got.shape[0] == wanted, f"step {s['step']}: {got.shape[0]} rows written, {wanted} wanted"
+        r = 0
+        for e in s["entries"]:
+            key = e["id"][strip:]
+            start = pos.get(e["id"], 0)
+            ref = ref_logits[key]
+            scale = float(ref.abs().max())
+            for w in e["want"]:
+                exp = ref[start + w].to(torch.float32).numpy()
+                err = float(np.abs(got[r] - exp).max()) / scale
+                if not np.isfinite(got[r]).all():
+                    err = float("inf")
+                if err > worst:
+                    worst, where = err, (s["step"], e["id"], start + w)
+                agree += int(got[r].argmax() == exp.argmax())
+                total += 1
+                r += 1
+            pos[e["id"]] = start + len(e["tokens"])
+    return worst, where, agree / max(total, 1)
