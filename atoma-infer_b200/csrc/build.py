@@ -47,7 +47,7 @@ def find_nvcc() -> str:
 def _digest(paths: Sequence[str], extra: str) -> str:
     h = hashlib.sha256(extra.encode())
     for p in paths:
-        h.update(p.encode())
+        h.update(os.path.relpath(p, CSRC).encode())  # the same name wherever the checkout lies
         with open(p, "rb") as f:
             h.update(f.read())
     return h.hexdigest()[:16]
@@ -120,3 +120,10 @@ HOST_SOURCES = ["host/capi.cpp", "host/cache_manager.cpp", "host/scheduler.cpp"]
 
 def host_library() -> ctypes.CDLL:
     return load_library("host", HOST_SOURCES, cuda=False)
+
+
+def all_kernel_libraries():
+    """(name, sources, defines) of every kernel library, for the build check."""
+    from .ops import CORE_SOURCES
+
+    return [("core", CORE_SOURCES, None)]

@@ -88,13 +88,14 @@ class StepFunction:
             if e.req in seen:
                 raise ValueError(f"request {e.req} appears twice in one step")
             seen.add(e.req)
-            is_new = not mgr.has_request(e.req)
-            slot = mgr.add_request(e.req) if is_new else mgr.state_slot(e.req)
+            added = not mgr.has_request(e.req)
+            slot = mgr.add_request(e.req) if added else mgr.state_slot(e.req)
             ctx_len = mgr.num_tokens(e.req)
+            is_new = ctx_len == 0  # also a request that a scheduler admitted (again) and that has run nothing yet
             try:
                 mgr.reserve(e.req, ctx_len + n)
             except Exception:
-                if is_new:
+                if added:
                     mgr.free_request(e.req)
                 raise
             for w in e.want:

@@ -1,0 +1,50 @@
+"""Sampling a token for each wanted row of logits, on the device.
+
+One kernel launch samples all rows (csrc/kernels/sampling.cu); per-row parameters
+travel in one small buffer, only token ids come back.  The random number of a
+request's n-th token depends on its seed and n alone (the reference gives every
+request a generator of its own, backends/vllm/src/llm_service.rs:371-372), so a
+request's tokens do not depend on who shares its batch, nor on preemption.
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from .params import ResolvedParams
+
+
+class Sampler:
+    def __init__(self, rt):
+        self.rt = rt
+        self._pinned = torch.cuda.is_available()
+
+    def sample(self, logits: torch.Tensor, params: Sequence[ResolvedParams], steps: Sequence[int],
+               histories: Sequence[Sequence[int]]) -> List[int]:
+        """``logits`` [R, vocab] float32 on the device; ``steps[i]``: how many tokens request i
+        has sampled before; ``histories[i]``: its tokens so far (for the repetition penalty)."""
+        R = logits.shape[0]
+        if R == 0:
+            return []
+        ops, dev = self.rt.ops, self.rt.device
+        for i, p in enumerate(params):
+            if p.repetition_penalty != 1.0:
+                ctx = list(histories[i])[-p.repeat_last_n:]
+                if ctx:
+                    ops.repeat_penalty(logits[i], p.repetition_penalty,
+                                       torch.tensor(ctx, dtype=torch.int32).to(dev, non_blocking=True))
+        # one buffer: seed u64 | step u64 | temperature f32 | top_k i32 | top_p f32 (64-bit arrays first: aligned)
+        host = torch.empty(7 * R, dtype=torch.int32, pin_memory=self._pinned)
+        h = host.numpy()
+        h[0:2 * R].view(np.uint64)[:] = [p.seed for p in params]
+        h[2 * R:4 * R].view(np.uint64)[:] = list(steps)
+        h[4 * R:5 * R].view(np.float32)[:] = [0.0 if p.greedy else p.temperature for p in params]
+        h[5 * R:6 * R] = [p.top_k for p in params]
+        h[6 * R:7 * R].view(np.float32)[:] = [p.top_p for p in params]
+        d = host.to(dev, non_blocking=True)
+        out = torch.empty(R, dtype=torch.int32, device=dev)
+        ops.sample(logits, d[4 * R:5 * R].view(torch.float32), d[5 * R:6 * R], d[6 * R:7 * R].view(torch.float32),
+                   d[0:2 * R], d[2 * R:4 * R], out)
+        return out.tolist()

@@ -21,7 +21,9 @@ from .safetensors_io import write_safetensors
 
 def _generator(seed: int, name: str, device="cpu") -> torch.Generator:
     g = torch.Generator(device=device)
-    g.manual_seed(((seed & 0xFFFFFFFF) << 32) ^ zlib.crc32(name.encode()))
+    # both halves depend on seed and name (the CPU generator seeds from the low 32 bits alone)
+    key = f"{seed}:{name}".encode()
+    g.manual_seed((zlib.crc32(key[::-1]) << 32) | zlib.crc32(key))
     return g
 
 
