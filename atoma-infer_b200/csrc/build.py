@@ -124,6 +124,7 @@ def host_library() -> ctypes.CDLL:
 
 def all_kernel_libraries():
     """(name, sources, defines) of every kernel library, for the build check."""
-    from .ops import CORE_SOURCES
+    from .ops import ATTENTION_HEAD_DIMS, ATTENTION_SOURCES, CORE_SOURCES
 
-    return [("core", CORE_SOURCES, None)]
+    return [("core", CORE_SOURCES, None)] + [
+        (f"attention_d{d}", ATTENTION_SOURCES, {"HEAD_DIM": d}) for d in ATTENTION_HEAD_DIMS]

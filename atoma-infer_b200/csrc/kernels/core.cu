@@ -312,15 +312,23 @@ extern "C" int attn_generic(const void* q, int q_stride, const void* cache, int 
     size_t smem = (size_t)(d + ATTN_KT + 40 + ATTN_KT * (d + 1)) * sizeof(float);
     dim3 grid(T, nq);
     cudaError_t e;
+    // the attribute only ever grows, and is not set again inside a stream capture once it is large enough
+    static size_t configured_f32 = 0, configured_bf16 = 0;
     if (dtype == DT_F32) {
-        e = cudaFuncSetAttribute(attn_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
+        if (smem > configured_f32) {
+            e = cudaFuncSetAttribute(attn_generic_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            configured_f32 = smem;
+        }
         attn_generic_kernel<float><<<grid, ATTN_THREADS, smem, stream>>>(
             (const float*)q, q_stride, (const float*)cache, L, meta, group, token_entry, positions, (float*)out, nq,
             window, scale, num_pages, status);
     } else {
-        e = cudaFuncSetAttribute(attn_generic_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
+        if (smem > configured_bf16) {
+            e = cudaFuncSetAttribute(attn_generic_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            configured_bf16 = smem;
+        }
         attn_generic_kernel<__nv_bfloat16><<<grid, ATTN_THREADS, smem, stream>>>(
             (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, L, meta, group, token_entry, positions,
             (__nv_bfloat16*)out, nq, window, scale, num_pages, status);

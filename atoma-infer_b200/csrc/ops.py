@@ -23,6 +23,8 @@ STATUS_WORDS = 4
 SKINNY_MAX_ROWS = 16  # bfloat16 linears with at most this many rows stream the weights
 
 CORE_SOURCES = ["kernels/core.cu", "kernels/linear_bf16.cu", "kernels/sampling.cu"]
+ATTENTION_SOURCES = ["kernels/attention_bf16.cu"]
+ATTENTION_HEAD_DIMS = (16, 64, 128)  # built by the build check; other head sizes are built when a model needs them
 
 
 class KernelError(RuntimeError):
@@ -51,6 +53,8 @@ class CudaOps:
         self.lib = build.load_library("core", CORE_SOURCES, cuda=True)
         self.status = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=self.device)
         self.launches = 0  # own kernel launches, counted for the benchmark record
+        self._attn_libs = {}
+        self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
 
     # ------------------------------------------------------------------ helpers
     def _stream(self):
@@ -124,11 +128,55 @@ class CudaOps:
                                            _p(inv_freq), _p(cache_layer), num_pages, T, nq, nkv, d, rot, page_size,
                                            int(store_kv), _p(self.status), self._stream()), "rope_kv_store")
 
-    def attention(self, q, q_stride: int, cache_layer, meta, group: int, token_entry, positions, out, T: int, nq: int,
-                  nkv: int, d: int, page_size: int, num_pages: int, window: int, scale: float):
-        self._check(self.lib.attn_generic(_p(q), q_stride, _p(cache_layer), _code(q), _p(meta), group, _p(token_entry),
-                                          _p(positions), _p(out), T, nq, nkv, d, page_size, num_pages, window,
-                                          ctypes.c_float(scale), _p(self.status), self._stream()), "attn_generic")
+    def attention(self, q, q_stride: int, cache_layer, ctx, group: int, out, nq: int, nkv: int, d: int,
+                  page_size: int, num_pages: int, window: int, scale: float):
+        """Attention of the step's queries over what their requests have cached (the step's own
+        keys included).  bfloat16 with a head size in steps of 16 up to 256 runs the tensor-core
+        kernels (one library per head size, built at first use); anything else, and all of
+        float32, runs the plain kernel."""
+        T, S = ctx.T, ctx.S
+        groups_ok = nq % nkv == 0 and nq // nkv <= 16
+        if q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and groups_ok and q_stride % 8 == 0:
+            lib = self._attention_library(d)
+            if ctx.decode_only:
+                splits = self.decode_splits(S, nkv, ctx.max_context)
+                n = lib.attn_decode_scratch_floats(S, nq, splits)
+                scratch = torch.empty(n, dtype=torch.float32, device=q.device) if n else None
+                self._check(lib.attn_decode(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
+                                            _p(ctx.positions), _p(out), _p(scratch), S, nq, nkv, page_size, num_pages,
+                                            window, ctypes.c_float(scale), splits, _p(self.status), self._stream()),
+                            "attn_decode")
+                self.launches += int(splits > 1)
+            else:
+                self._check(lib.attn_prefill(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
+                                             _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
+                                             page_size, num_pages, window, ctypes.c_float(scale), _p(self.status),
+                                             self._stream()), "attn_prefill")
+            return
+        if d > 256:
+            raise KernelError(f"head size {d} is not supported (at most 256)")
+        self._check(self.lib.attn_generic(_p(q), q_stride, _p(cache_layer), _code(q), _p(ctx.meta), group,
+                                          _p(ctx.token_entry), _p(ctx.positions), _p(out), T, nq, nkv, d, page_size,
+                                          num_pages, window, ctypes.c_float(scale), _p(self.status), self._stream()),
+                    "attn_generic")
+
+    def _attention_library(self, d: int):
+        lib = self._attn_libs.get(d)
+        if lib is None:
+            lib = build.load_library(f"attention_d{d}", ATTENTION_SOURCES, cuda=True, defines={"HEAD_DIM": d})
+            lib.attn_decode_scratch_floats.restype = ctypes.c_size_t
+            if lib.attn_head_dim() != d:
+                raise KernelError(f"attention library was built for head size {lib.attn_head_dim()}, wanted {d}")
+            self._attn_libs[d] = lib
+        return lib
+
+    def decode_splits(self, S: int, nkv: int, max_context: int) -> int:
+        """Splits of the key range per (request, key/value head) in a decode step: enough blocks
+        for two per SM, each with at least 256 keys, at most 32."""
+        blocks = max(S * nkv, 1)
+        by_sm = -(-2 * self.num_sms // blocks)
+        by_len = max(1, max_context // 256)
+        return max(1, min(by_sm, by_len, 32))
 
     def sample(self, logits, temperature, top_k, top_p, seed, step, out, num_rows=None):
         R, V = logits.shape

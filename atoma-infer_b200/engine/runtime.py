@@ -50,7 +50,8 @@ def make_runtime(dtype: str, device=None, ops=None) -> Runtime:
 
 def load_model(model_dir: str, *, dtype: str = "bfloat16", device=None, page_size: int = 16,
                num_pages: Optional[int] = None, max_seqs: int = 64, gpu_memory_utilization: float = 0.9,
-               poison_cache: bool = False, ops=None) -> LoadedModel:
+               poison_cache: bool = False, ops=None, cuda_graphs: bool = False,
+               max_model_len: Optional[int] = None) -> LoadedModel:
     """``num_pages``: usable pages per pool; None sizes the pools from free device memory."""
     arch, config = architecture_of(model_dir)
     spec = arch.build_spec(config)
@@ -70,5 +71,6 @@ def load_model(model_dir: str, *, dtype: str = "bfloat16", device=None, page_siz
         g.num_pages = num_pages + 1  # page 0 is never handed out
     manager = CacheManager(page_size, groups, max_seqs)
     cache = KVCache(model, groups, page_size, max_seqs, rt, poison=poison_cache)
-    step = StepFunction(model, cache, manager, rt)
+    limit = min(max_model_len or spec.max_position or 1 << 30, num_pages * page_size)
+    step = StepFunction(model, cache, manager, rt, cuda_graphs=cuda_graphs, max_model_len=limit)
     return LoadedModel(config, model, rt, manager, cache, step, page_size, num_pages)

@@ -63,20 +63,29 @@ class MetaLayout:
 
 
 class StepFunction:
-    def __init__(self, model, cache: KVCache, manager: CacheManager, rt: Runtime):
+    def __init__(self, model, cache: KVCache, manager: CacheManager, rt: Runtime, cuda_graphs: bool = False,
+                 max_model_len: int = 0):
         if len(manager.groups) > MAX_GROUPS:
             raise ValueError(f"at most {MAX_GROUPS} cache groups are supported")
         self.model, self.cache, self.manager, self.rt = model, cache, manager, rt
         self.page_size = manager.page_size
         self._pinned = torch.cuda.is_available()
         self.steps = 0
+        # Decode steps (every request brings one token and wants its logits) replay a CUDA graph
+        # captured per padded batch size; the reference has no graphs.
+        self.cuda_graphs = cuda_graphs and torch.cuda.is_available() and getattr(model, "graph_safe", True)
+        self.max_model_len = max_model_len
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ metadata
     def _host_buffer(self, n: int) -> torch.Tensor:
         return torch.empty(n, dtype=torch.int32, pin_memory=self._pinned)
 
-    def prepare(self, entries: Sequence[StepEntry]):
-        """Claims pages, builds the metadata on the host.  Returns (host buffer, layout, infos, R)."""
+    def prepare(self, entries: Sequence[StepEntry], pad_to: int = 0):
+        """Claims pages, builds the metadata on the host.  Returns (host buffer, layout, infos, R).
+        ``pad_to``: lay the arrays out for that many tokens, entries and rows (a captured graph's
+        fixed sizes); the header still holds the true counts, which is what the kernels obey."""
         mgr, ps = self.manager, self.page_size
         infos: List[EntryInfo] = []
         seen = set()
@@ -106,7 +115,7 @@ class StepFunction:
         T, S = start, len(infos)
         R = sum(len(e.want) for e in entries)
         strides = tuple(max((mgr.table_len(i.req, g) for i in infos), default=1) for g in range(len(mgr.groups)))
-        lay = MetaLayout(T, S, R, strides)
+        lay = MetaLayout(max(T, pad_to), max(S, pad_to), max(R, pad_to), strides)
         host = self._host_buffer(lay.size)
         h = host.numpy()
         h[:META_HEADER_INTS] = 0
@@ -121,13 +130,19 @@ class StepFunction:
             h[lay.ctx + k] = i.context_len
             h[lay.slots + k] = i.state_slot
             rows += [a + w for w in e.want]
-        h[lay.cu + S] = T
+        h[lay.cu + S:lay.cu + lay.S + 1] = T
+        h[lay.tokens + T:lay.tokens + lay.T] = 0
+        h[lay.positions + T:lay.positions + lay.T] = 0
+        h[lay.token_entry + T:lay.token_entry + lay.T] = 0
+        h[lay.ctx + S:lay.ctx + lay.S] = 0
+        h[lay.slots + S:lay.slots + lay.S] = 0
+        h[lay.rows:lay.rows + max(lay.R, 1)] = 0
         if rows:
             h[lay.rows:lay.rows + R] = rows
         base = h.ctypes.data
         for g, (off, stride) in enumerate(zip(lay.tables, strides)):
             h[META_BT_STRIDE + g], h[META_BT_OFFSET + g] = stride, off
-            h[off:off + S * stride] = -1
+            h[off:off + lay.S * stride] = -1
             for k, i in enumerate(infos):
                 mgr.table_into(i.req, g, base + 4 * (off + k * stride), stride)
         return host, lay, infos, R
@@ -151,6 +166,8 @@ class StepFunction:
         order of the entries and of their ``want`` lists."""
         if not entries:
             return torch.empty((0, self.model.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
+        if self._graph_eligible(entries):
+            return self._run_graph(entries)
         host, lay, infos, R = self.prepare(entries)
         dev = host.to(self.rt.device, non_blocking=True)
         for i in infos:
@@ -163,6 +180,62 @@ class StepFunction:
         self.steps += 1
         return logits
 
+    # ------------------------------------------------------------------ decode steps as CUDA graphs
+    GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+    def _graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
+        if not self.cuda_graphs or len(entries) > self.GRAPH_BUCKETS[-1] or self.cache.state:
+            return False
+        return all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+
+    def _run_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        S = len(entries)
+        bucket = next(b for b in self.GRAPH_BUCKETS if b >= S)
+        g = self._graphs.get(bucket)
+        if g is None:
+            cap_stride = -(-max(self.max_model_len, 1) // self.page_size)
+            cap = MetaLayout(bucket, bucket, bucket, (cap_stride,) * len(self.manager.groups)).size
+            g = self._graphs[bucket] = _DecodeGraph(torch.zeros(cap, dtype=torch.int32, device=self.rt.device), cap_stride)
+        host, lay, infos, R = self.prepare(entries, pad_to=bucket)
+        if max(lay.strides, default=0) > g.cap_stride:
+            raise RuntimeError(f"a request holds more pages than max_model_len ({self.max_model_len}) allows")
+        g.meta[:lay.size].copy_(host, non_blocking=True)
+        if g.graph is None:
+            ctx = self.context(g.meta, lay, [])
+            # sizes that pick kernels and splits are those of the bucket, not of this batch
+            ctx.decode_only, ctx.max_tokens_per_entry, ctx.max_context = True, 1, max(self.max_model_len, 1)
+            rows = g.meta[lay.rows:lay.rows + bucket]
+            if not g.warm:  # the first step of a bucket runs eagerly: libraries load, attributes get set
+                logits = self.model.forward(ctx, self.cache, rows, bucket)
+                g.warm = True
+            else:
+                torch.cuda.synchronize(self.rt.device)
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    g.logits = self.model.forward(ctx, self.cache, rows, bucket)
+                g.graph = graph
+                graph.replay()
+                logits = g.logits
+        else:
+            g.graph.replay()
+            self.graph_replays += 1
+            logits = g.logits
+        for i in infos:
+            self.manager.advance(i.req, i.num_tokens)
+        self.steps += 1
+        return logits[:S]
+
     def finish(self, req: int) -> None:
         """The request ends: its pages and its state slot go back to the pools."""
         self.manager.free_request(req)
+
+
+class _DecodeGraph:
+    """A captured decode step for one padded batch size: its metadata buffer (fixed address,
+    rewritten before every replay) and its logits buffer."""
+
+    def __init__(self, meta: torch.Tensor, cap_stride: int):
+        self.meta, self.cap_stride = meta, cap_stride
+        self.graph = None
+        self.logits = None
+        self.warm = False

@@ -33,7 +33,7 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, stream: IO
     unit = max(ROUND_TOKENS, page_size)
     num_pages = ((max_tokens + unit - 1) // unit) * unit // page_size
     lm = load_model(model_dir, dtype=dtype, device=device, page_size=page_size, num_pages=num_pages,
-                    max_seqs=max_live, poison_cache=True, ops=ops)
+                    max_seqs=max_live, poison_cache=True, ops=ops, cuda_graphs=True)
     ids: Dict[str, int] = {}
     next_id = 0
     steps = 0

@@ -25,6 +25,8 @@ from .base import Mixer
 
 
 class Attention(Mixer):
+    graph_safe = True  # reads the step's metadata on the device only
+
     def __init__(self, params, prefix):
         super().__init__(params, prefix)
         p = params
@@ -75,9 +77,8 @@ class Attention(Mixer):
         self.position.encode_and_store(qkv, ctx, cache, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
                                        head_dim=self.head_dim)
         out = torch.empty((ctx.T, self.q_size), dtype=x.dtype, device=x.device)
-        ops.attention(qkv, qkv.shape[1], cache.pages, ctx.meta, cache.group, ctx.token_entry, ctx.positions, out,
-                      ctx.T, self.num_heads, self.num_kv_heads, self.head_dim, cache.page_size, cache.num_pages,
-                      int(self.window or 0), self.scale)
+        ops.attention(qkv, qkv.shape[1], cache.pages, ctx, cache.group, out, self.num_heads, self.num_kv_heads,
+                      self.head_dim, cache.page_size, cache.num_pages, int(self.window or 0), self.scale)
         return ops.linear(out, self.w_o, meta=ctx.meta)
 
 

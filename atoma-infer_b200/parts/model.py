@@ -104,6 +104,8 @@ class DecoderModel:
             self.layer_group[layer] = (gi, len(self.groups[gi].layers))
             self.groups[gi].layers.append(layer)
         self.state_bytes = [blk.mixer.state_bytes() for blk in self.blocks]
+        # a step of this model can be captured in a CUDA graph if no part reads the host-side entry list
+        self.graph_safe = all(getattr(blk.mixer, "graph_safe", False) for blk in self.blocks)
 
     def declare(self) -> List[TensorDecl]:
         return declared_tensors(self.spec)

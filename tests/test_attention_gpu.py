@@ -1,0 +1,128 @@
+"""The attention kernels alone against the plain attention, at sizes other than the engine tests use:
+head sizes 16..256, several group sizes and page sizes, contexts already in the cache, windows,
+split key ranges, pages in scrambled physical order, a never-written (NaN) rest of the cache."""
+import math
+
+import pytest
+import torch
+
+import kernel_utils as K
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def rts():
+    from atoma_infer_b200.engine.runtime import make_runtime
+
+    return {"bfloat16": make_runtime("bfloat16", "cuda:0"), "float32": make_runtime("float32", "cuda:0")}
+
+
+def run_attention(rt, entries, nq, nkv, d, page_size, window=None, seed=0, scale=None, splits=None, stand_out=None):
+    """entries: (context_len, num_tokens).  Returns (engine output, plain output) lists per request,
+    each [num_tokens, nq, d]."""
+    g = torch.Generator().manual_seed(seed)
+    lengths = [c + n for c, n in entries]
+    tables, num_pages = K.scrambled_tables(lengths, page_size, seed)
+    dt = rt.dtype
+    qs = [torch.randn(L, nq, d, generator=g) for L in lengths]
+    ks = [torch.randn(L, nkv, d, generator=g) for L in lengths]
+    vs = [torch.randn(L, nkv, d, generator=g) for L in lengths]
+    if stand_out is not None:  # one far key that the last query must find among all the others
+        for q, k in zip(qs, ks):
+            k[stand_out] *= 4.0
+            q[-1] = k[stand_out].repeat_interleave(nq // nkv, dim=0) * 1.5
+    qs, ks, vs = ([t.to(dt).float() for t in x] for x in (qs, ks, vs))  # the values the kernels will see
+    cache = torch.full((num_pages, 2, nkv, page_size, d), float("nan"), dtype=dt, device=rt.device)
+    K.fill_cache(cache, tables, ks, vs, page_size)
+    ctx, _ = K.make_context(rt, entries, page_size, tables)
+    T = ctx.T
+    qkv = torch.zeros(T, (nq + 2 * nkv) * d, dtype=dt, device=rt.device)
+    row = 0
+    for (c, n), q in zip(entries, qs):
+        qkv[row:row + n, :nq * d] = q[c:c + n].reshape(n, nq * d).to(dt)
+        row += n
+    out = torch.full((T, nq * d), float("nan"), dtype=dt, device=rt.device)
+    scale = scale or 1.0 / math.sqrt(d)
+    ops = rt.ops
+    if splits is not None:
+        ops.decode_splits = lambda *a: splits
+    try:
+        ops.attention(qkv, qkv.shape[1], cache, ctx, 0, out, nq, nkv, d, page_size, num_pages, int(window or 0), scale)
+    finally:
+        if splits is not None:
+            del ops.decode_splits
+    ops.check_status()
+    got, want, row = [], [], 0
+    for (c, n), q, k, v in zip(entries, qs, ks, vs):
+        got.append(out[row:row + n].float().cpu().reshape(n, nq, d))
+        want.append(P.causal_attention(q.double(), k.double(), v.double(), scale, window)[c:c + n].float())
+        row += n
+    return got, want
+
+
+def worst(got, want):
+    return max(float((a - b).abs().max()) for a, b in zip(got, want))
+
+
+@pytest.mark.parametrize("d,nq,nkv,page", [(16, 4, 2, 4), (64, 3, 1, 8), (64, 32, 8, 16), (128, 8, 8, 16),
+                                           (32, 6, 2, 64), (48, 5, 5, 16), (80, 16, 2, 16), (256, 2, 1, 16)])
+def test_prefill_with_cached_context_bf16(rts, d, nq, nkv, page):
+    entries = [(0, 70), (37, 29), (130, 2), (64, 1), (5, 131)]
+    got, want = run_attention(rts["bfloat16"], entries, nq, nkv, d, page, seed=d)
+    assert worst(got, want) < 2e-2  # values are O(1); bfloat16 P and outputs
+
+
+@pytest.mark.parametrize("d,nq,nkv,page,splits", [(64, 32, 8, 16, 1), (64, 32, 8, 16, 5), (128, 8, 2, 16, 3),
+                                                  (16, 4, 2, 4, 2), (64, 3, 1, 8, 4), (256, 4, 1, 16, 2),
+                                                  (96, 12, 4, 32, 7)])
+def test_decode_with_splits_bf16(rts, d, nq, nkv, page, splits):
+    entries = [(0, 1), (1, 1), (31, 1), (32, 1), (300, 1), (777, 1), (63, 1)]
+    got, want = run_attention(rts["bfloat16"], entries, nq, nkv, d, page, seed=splits, splits=splits)
+    assert worst(got, want) < 2e-2
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 100])
+def test_window_bf16_and_float32(rts, window):
+    for dtype, tol in (("bfloat16", 2e-2), ("float32", 2e-5)):
+        got, want = run_attention(rts[dtype], [(0, 150), (90, 40), (200, 3)], 4, 2, 64, 16, window=window, seed=window)
+        assert worst(got, want) < tol, dtype
+        got, want = run_attention(rts[dtype], [(0, 1), (99, 1), (100, 1), (340, 1)], 4, 2, 64, 16, window=window,
+                                  seed=window, splits=3 if dtype == "bfloat16" else None)
+        assert worst(got, want) < tol, dtype
+
+
+@pytest.mark.parametrize("d,nq,nkv,page", [(16, 4, 2, 4), (64, 3, 1, 8), (40, 2, 2, 16), (200, 2, 1, 16), (256, 2, 2, 4)])
+def test_plain_kernel_float32_any_head_size(rts, d, nq, nkv, page):
+    entries = [(0, 70), (37, 29), (130, 2), (64, 1)]
+    got, want = run_attention(rts["float32"], entries, nq, nkv, d, page, seed=d)
+    assert worst(got, want) < 2e-5
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_a_far_key_among_hundreds_is_found(rts, dtype):
+    """The last query matches one key far back; if any page or tile were skipped or misplaced the
+    output would be an average of values instead of (almost) that key's value."""
+    for far in (3, 64, 255, 256, 511):
+        got, want = run_attention(rts[dtype], [(0, 600)], 4, 2, 64, 16, seed=far, stand_out=far, scale=1.0)
+        assert worst(got, want) < (3e-2 if dtype == "bfloat16" else 1e-4)
+        got, want = run_attention(rts[dtype], [(599, 1)], 4, 2, 64, 16, seed=far, stand_out=far, scale=1.0,
+                                  splits=4 if dtype == "bfloat16" else None)
+        assert worst(got, want) < (3e-2 if dtype == "bfloat16" else 1e-4)
+
+
+def test_float32_attention_is_bitwise_independent_of_cutting(rts):
+    """The same query gives the same bits whether it comes alone, in a portion, or beside others."""
+    rt = rts["float32"]
+    whole, _ = run_attention(rt, [(0, 90)], 4, 2, 64, 8, seed=7)
+    tail, _ = run_attention(rt, [(60, 30)], 4, 2, 64, 8, seed=7)
+    single, _ = run_attention(rt, [(89, 1)], 4, 2, 64, 8, seed=7)
+    assert torch.equal(whole[0][60:], tail[0]) and torch.equal(whole[0][89:], single[0])
+
+
+def test_head_sizes_beyond_the_kernels_are_refused(rts):
+    from atoma_infer_b200.csrc.ops import KernelError
+
+    with pytest.raises(KernelError):
+        run_attention(rts["bfloat16"], [(0, 4)], 1, 1, 272, 16)
