@@ -65,28 +65,56 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// Loads `rows` key (kv = 0) or value (kv = 1) rows, positions k0 .. k0+rows-1 of one
-// request and head, into a tile [rows][LDS].  Positions outside [lo, hi) are zero
-// filled (a value row of a page nobody wrote must not reach P*V, even times zero).
-__device__ __forceinline__ void load_kv_tile(bf16* tile, const bf16* __restrict__ cache, const CacheLayout& L,
-                                             const int* __restrict__ bt, int num_pages, int kvh, int kv, int k0,
-                                             int rows, int lo, int hi, int tid, int nthreads, int* status) {
-    constexpr int CHUNKS = D / 8;  // 16-byte chunks per row
-    for (int idx = tid; idx < rows * CHUNKS; idx += nthreads) {
-        int r = idx / CHUNKS, c = idx % CHUNKS;
-        int pos = k0 + r;
-        bf16* dst = tile + r * LDS + c * 8;
-        bool ok = pos >= lo && pos < hi;
-        if (ok) {
-            int page = bt[pos / L.page_size];
-            if (page <= 0 || page >= num_pages) {
-                atomicExch(&status[STATUS_BAD_PAGE], 1 + pos);
-                ok = false;
-            } else {
-                cp_async_16(dst, cache + L.offset(page, kv, kvh, pos % L.page_size) + c * 8);
-            }
+// Copies the block-table entries of pages page_lo .. page_lo+count-1 into shared memory, once
+// per block: a tile load then finds its pages without a dependent global load per row.
+// An entry that names no valid page becomes -1 and raises the status word.
+__device__ __forceinline__ void stage_block_table(int* bt_s, const int* __restrict__ bt, int page_lo, int count,
+                                                  int num_pages, int tid, int nthreads, int* status) {
+    for (int i = tid; i < count; i += nthreads) {
+        int page = bt[page_lo + i];
+        if (page <= 0 || page >= num_pages) {
+            atomicExch(&status[STATUS_BAD_PAGE], 1 + (page_lo + i));
+            page = -1;
         }
-        if (!ok) *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+        bt_s[i] = page;
+    }
+}
+
+// Loads `rows` key rows into ktile and value rows into vtile ([rows][LDS] each), positions
+// k0 .. k0+rows-1 of one request and head.  Positions outside [lo, hi) are zero filled (a
+// value row of a page nobody wrote must not reach P*V, even times zero).
+__device__ __forceinline__ void load_kv_tile(bf16* ktile, bf16* vtile, const bf16* __restrict__ cache,
+                                             const CacheLayout& L, const int* bt_s, int page_lo, int kvh, int k0,
+                                             int rows, int lo, int hi, int tid, int nthreads) {
+    constexpr int PAIRS = D / 16;  // 32-byte sectors per row: one address computation serves four copies
+    const int ps = L.page_size;
+    const int ps_shift = (ps & (ps - 1)) == 0 ? 31 - __clz(ps) : -1;
+    const size_t v_off = (size_t)L.num_kv_heads * ps * D;  // from a page's K block to its V block
+    const size_t page_stride = 2 * v_off, head_off = (size_t)kvh * ps * D;
+    for (int idx = tid; idx < rows * PAIRS; idx += nthreads) {
+        int r = idx / PAIRS, c = (idx % PAIRS) * 16;
+        int pos = k0 + r;
+        bf16* kd = ktile + r * LDS + c;
+        bf16* vd = vtile + r * LDS + c;
+        int page = -1, slot = 0;
+        if (pos >= lo && pos < hi) {
+            int pidx = ps_shift >= 0 ? pos >> ps_shift : pos / ps;
+            slot = pos - pidx * ps;
+            page = bt_s[pidx - page_lo];
+        }
+        if (page > 0) {
+            const bf16* src = cache + (size_t)page * page_stride + head_off + (size_t)slot * D + c;
+            cp_async_16(kd, src);
+            cp_async_16(kd + 8, src + 8);
+            cp_async_16(vd, src + v_off);
+            cp_async_16(vd + 8, src + v_off + 8);
+        } else {
+            uint4 z = make_uint4(0u, 0u, 0u, 0u);
+            *reinterpret_cast<uint4*>(kd) = z;
+            *reinterpret_cast<uint4*>(kd + 8) = z;
+            *reinterpret_cast<uint4*>(vd) = z;
+            *reinterpret_cast<uint4*>(vd + 8) = z;
+        }
     }
 }
 
@@ -184,6 +212,7 @@ constexpr size_t DEC_TILE_BYTES = (size_t)(16 * LDS + DEC_WARPS * DEC_WARP_ELEMS
 constexpr size_t DEC_MERGE_BYTES = (size_t)DEC_WARPS * (32 + 16 * D) * sizeof(float);
 constexpr size_t DEC_SMEM = 16 * LDS * sizeof(bf16) +
     (DEC_WARPS * DEC_WARP_ELEMS * sizeof(bf16) > DEC_MERGE_BYTES ? DEC_WARPS * DEC_WARP_ELEMS * sizeof(bf16) : DEC_MERGE_BYTES);
+// + a slice of the block table, sized by the host (bt_cap entries)
 }  // namespace
 
 __global__ void __launch_bounds__(DEC_WARPS * 32)
@@ -191,10 +220,11 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    const int* __restrict__ meta, int group, const int* __restrict__ cu_tokens,
                    const int* __restrict__ positions, bf16* __restrict__ out, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int nq, int window, float scale_log2, int num_pages, int splits,
-                   int* __restrict__ status) {
+                   int bt_cap, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* qtile = reinterpret_cast<bf16*>(smem_raw);
     bf16* tiles = qtile + 16 * LDS;
+    int* bt_s = reinterpret_cast<int*>(smem_raw + DEC_SMEM);
     const int split = blockIdx.x, kvh = blockIdx.y, e = blockIdx.z;
     if (e >= meta[META_NUM_ENTRIES]) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -205,6 +235,14 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     const int per = (((kv_len - kstart + splits - 1) / splits + DEC_KT - 1) / DEC_KT) * DEC_KT;
     const int lo = kstart + split * per, hi = min(kv_len, lo + per);
     const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)e * meta[META_BT_STRIDE + group];
+    const int page_lo = lo / L.page_size;
+    int page_cnt = lo < hi ? (hi - 1) / L.page_size - page_lo + 1 : 0;
+    if (page_cnt > bt_cap) {  // the host sized the slice for a shorter context than this request has
+        if (tid == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + hi);
+        page_cnt = bt_cap;
+    }
+    stage_block_table(bt_s, bt, page_lo, page_cnt, num_pages, tid, DEC_WARPS * 32, status);
+    const int hi_s = min(hi, (page_lo + page_cnt) * L.page_size);  // never beyond the staged slice
 
     for (int idx = tid; idx < 16 * (D / 8); idx += DEC_WARPS * 32) {
         int r = idx / (D / 8), c = idx % (D / 8);
@@ -227,8 +265,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     const int ntiles = lo < hi ? (hi - lo + DEC_KT - 1) / DEC_KT : 0;
     auto load_tile = [&](int t, int stage) {
         bf16* k = mine + stage * 2 * DEC_KT * LDS;
-        load_kv_tile(k, cache, L, bt, num_pages, kvh, 0, lo + t * DEC_KT, DEC_KT, lo, hi, lane, 32, status);
-        load_kv_tile(k + DEC_KT * LDS, cache, L, bt, num_pages, kvh, 1, lo + t * DEC_KT, DEC_KT, lo, hi, lane, 32, status);
+        load_kv_tile(k, k + DEC_KT * LDS, cache, L, bt_s, page_lo, kvh, lo + t * DEC_KT, DEC_KT, lo, hi_s, lane, 32);
     };
     if (warp < ntiles) load_tile(warp, 0);
     cp_async_commit();
@@ -339,10 +376,11 @@ __global__ void __launch_bounds__(128)
 attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache, CacheLayout L,
                     const int* __restrict__ meta, int group, const int* __restrict__ cu_tokens,
                     const int* __restrict__ ctx_lens, bf16* __restrict__ out, int nq, int window, float scale_log2,
-                    int num_pages, int* __restrict__ status) {
+                    int num_pages, int bt_cap, int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* qtile = reinterpret_cast<bf16*>(smem_raw);
     bf16* kv = qtile + PF_ROWS * LDS;
+    int* bt_s = reinterpret_cast<int*>(smem_raw + PF_SMEM);
     const int qt = blockIdx.x, kvh = blockIdx.y, e = blockIdx.z;
     if (e >= meta[META_NUM_ENTRIES]) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -366,14 +404,21 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     const int kbeg = window > 0 ? max(0, p_first - window + 1) : 0, kend = p_last + 1;
     const int k_first = (kbeg / PF_KT) * PF_KT;
     const int ntiles = (kend - k_first + PF_KT - 1) / PF_KT;
+    const int page_lo = kbeg / L.page_size;
+    int page_cnt = (kend - 1) / L.page_size - page_lo + 1;
+    if (page_cnt > bt_cap) {
+        if (tid == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + kend);
+        page_cnt = bt_cap;
+    }
+    stage_block_table(bt_s, bt, page_lo, page_cnt, num_pages, tid, 128, status);
+    const int kend_s = min(kend, (page_lo + page_cnt) * L.page_size);
+    __syncthreads();  // the Q tile and the table slice are written
     auto load_tile = [&](int t, int stage) {
         bf16* k = kv + stage * 2 * PF_KT * LDS;
-        load_kv_tile(k, cache, L, bt, num_pages, kvh, 0, k_first + t * PF_KT, PF_KT, kbeg, kend, tid, 128, status);
-        load_kv_tile(k + PF_KT * LDS, cache, L, bt, num_pages, kvh, 1, k_first + t * PF_KT, PF_KT, kbeg, kend, tid, 128, status);
+        load_kv_tile(k, k + PF_KT * LDS, cache, L, bt_s, page_lo, kvh, k_first + t * PF_KT, PF_KT, kbeg, kend_s, tid, 128);
     };
     load_tile(0, 0);
     cp_async_commit();
-    __syncthreads();  // the Q tile is written
     const bf16* qwarp = qtile + warp * 16 * LDS;
     uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
     if (Q_IN_REGS) {
@@ -451,43 +496,54 @@ extern "C" size_t attn_decode_scratch_floats(int S, int nq, int splits) {
 
 extern "C" int attn_prefill(const void* q, int q_stride, const void* cache, const int* meta, int group,
                             const int* cu_tokens, const int* ctx_lens, void* out, int S, int max_q_len, int nq, int nkv,
-                            int page_size, int num_pages, int window, float scale, int* status, cudaStream_t stream) {
+                            int page_size, int num_pages, int window, float scale, int max_context, int* status,
+                            cudaStream_t stream) {
     if (S <= 0 || max_q_len <= 0) return 0;
     if (nq % nkv || nq / nkv > PF_ROWS) return (int)cudaErrorInvalidValue;
     CacheLayout L{nkv, page_size, D};
     int tpt = PF_ROWS / (nq / nkv);
     dim3 grid((max_q_len + tpt - 1) / tpt, nkv, S);
-    static bool configured = false;  // once: the attribute is not set again inside a stream capture
-    if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PF_SMEM);
+    // block-table slice: the pages of the keys a tile can see (all of the context, or a window of it)
+    int span = window > 0 ? min(max_context, window + tpt + PF_KT) : max_context;
+    int bt_cap = span / page_size + 2;
+    size_t smem = PF_SMEM + (size_t)bt_cap * sizeof(int);
+    if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
+    static size_t configured = 0;  // grows only, and is not set again inside a stream capture once large enough
+    if (smem > configured) {
+        cudaError_t err = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
-        configured = true;
+        configured = smem;
     }
-    attn_prefill_kernel<<<grid, 128, PF_SMEM, stream>>>((const bf16*)q, q_stride, (const bf16*)cache, L, meta, group, cu_tokens,
-                                                         ctx_lens, (bf16*)out, nq, window, scale * LOG2E, num_pages, status);
+    attn_prefill_kernel<<<grid, 128, smem, stream>>>((const bf16*)q, q_stride, (const bf16*)cache, L, meta, group, cu_tokens,
+                                                      ctx_lens, (bf16*)out, nq, window, scale * LOG2E, num_pages, bt_cap, status);
     LAUNCH_RETURN();
 }
 
 extern "C" int attn_decode(const void* q, int q_stride, const void* cache, const int* meta, int group,
                            const int* cu_tokens, const int* positions, void* out, float* scratch, int S, int nq, int nkv,
-                           int page_size, int num_pages, int window, float scale, int splits, int* status,
-                           cudaStream_t stream) {
+                           int page_size, int num_pages, int window, float scale, int splits, int max_context,
+                           int* status, cudaStream_t stream) {
     if (S <= 0) return 0;
     if (nq % nkv || nq / nkv > 16 || splits < 1) return (int)cudaErrorInvalidValue;
     if (splits > 1 && !scratch) return (int)cudaErrorInvalidValue;
     CacheLayout L{nkv, page_size, D};
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)S * nq * splits * D : nullptr;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t err = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)DEC_SMEM);
+    int span = window > 0 ? min(max_context, window) : max_context;
+    int per = (((span + splits - 1) / splits + DEC_KT - 1) / DEC_KT) * DEC_KT;  // keys of one split at most
+    int bt_cap = per / page_size + 2;
+    size_t smem = DEC_SMEM + (size_t)bt_cap * sizeof(int);
+    if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
+    static size_t configured = 0;
+    if (smem > configured) {
+        cudaError_t err = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
-        configured = true;
+        configured = smem;
     }
     dim3 grid(splits, nkv, S);
-    attn_decode_kernel<<<grid, DEC_WARPS * 32, DEC_SMEM, stream>>>((const bf16*)q, q_stride, (const bf16*)cache, L, meta, group,
-                                                                   cu_tokens, positions, (bf16*)out, part_o, part_ml, nq,
-                                                                   window, scale * LOG2E, num_pages, splits, status);
+    attn_decode_kernel<<<grid, DEC_WARPS * 32, smem, stream>>>((const bf16*)q, q_stride, (const bf16*)cache, L, meta, group,
+                                                               cu_tokens, positions, (bf16*)out, part_o, part_ml, nq,
+                                                               window, scale * LOG2E, num_pages, splits, bt_cap, status);
     if (splits > 1) {
         dim3 cgrid(nq, S);
         attn_combine_kernel<<<cgrid, D < 128 ? D : 128, 0, stream>>>(part_o, part_ml, meta, cu_tokens, (bf16*)out, nq, splits);

@@ -1,125 +1,187 @@
 // Weight-streaming linear layer for few rows: y[M, N] = x[M, K] * w[N, K]^T, bfloat16 in,
 // float32 accumulate, bfloat16 or float32 out.
 //
-// A decode step multiplies a handful of rows by every weight matrix: the time is the
-// time to read the weights once.  Each warp owns COLS rows of w (output columns) and
-// streams them with 16-byte loads, 32 lanes side by side; the few rows of x come from
-// L1/L2.  A 128-row tensor-core tile would be nearly all padding here.  The reference
-// calls cuBLAS for these (models/src/llama.rs:269-271, 311, 364-365, 476).
+// A decode step multiplies a handful of rows by every weight matrix: its time is the
+// time to read the weights once, so the kernel is built around the weight stream.
+// The weights are the A operand of mma.sync m16n8k16 (16 weight rows = 16 output
+// columns per block), the few rows of x the B operand (8 per n-tile).  Every thread
+// fetches 16 contiguous bytes of a weight row per load, straight from global memory
+// into its fragment: the k index inside a 32-wide block is permuted the same way
+// for both operands, which a dot product does not notice.  The warps of a block
+// split K between them and add up through shared memory in a fixed order; when a
+// matrix has too few 16-row tiles to fill the GPU, the blocks of a thread-block
+// cluster split K further and the first block adds the others' partial sums from
+// their shared memory (distributed shared memory), again in a fixed order.  A
+// 128-row tensor-core tile would be nearly all padding here; the reference calls
+// cuBLAS for these products (models/src/llama.rs:269-271, 311, 364-365, 476).
 //
-// Optional epilogues: silu(gate) * up for a fused [gate; up] weight (out has N/2
-// columns), and float32 output for the logits.
+// Epilogues: plain; silu(gate) * up for a stacked [gate; up] weight (N/2 output
+// columns; a block then takes 8 gate rows and the 8 up rows that belong to them).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
-#define SK_ROWS 8   // rows of x per pass
-#define SK_COLS 2   // output columns per warp
-#define SK_WARPS 8
+namespace cg = cooperative_groups;
 
-struct alignas(16) bf16x8 { __nv_bfloat162 v[4]; };
+#define SM_WARPS 8        // warps of a block, splitting K
+#define SM_UNROLL 4       // 32-wide k blocks in flight per warp
+#define SM_MAX_ROWS 16    // rows of x (two n-tiles)
 
-template <typename TO, int EPI>  // EPI 0: plain, 1: silu(gate)*up with gate rows [0, N/2), up rows [N/2, N)
-__global__ void __launch_bounds__(SK_WARPS * 32)
-linear_skinny_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, TO* __restrict__ y,
-                     const int* __restrict__ meta, int use_rows, int M, int N, int K) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int m0 = blockIdx.y * SK_ROWS;
-    int m_live = use_rows ? meta[META_NUM_ROWS] : (meta ? meta[META_NUM_TOKENS] : M);
-    m_live = min(m_live, M);
-    if (m0 >= m_live) return;
-    const int rows = min(SK_ROWS, m_live - m0);
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <typename TO, int NT, int EPI>  // NT n-tiles of 8 rows of x; EPI 1: silu(gate) * up
+__global__ void __launch_bounds__(SM_WARPS * 32, 3)  // three blocks a multiprocessor: loads in flight
+linear_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, TO* __restrict__ y,
+                    int M, int N, int K, int ksplits) {
+    __shared__ float red[SM_WARPS][16][NT * 8 + 1];
+    __shared__ float part[16][NT * 8];  // this block's sum over its warps; read by the cluster's first block
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
     const int n_out = EPI == 1 ? N / 2 : N;
-    const int c0 = (blockIdx.x * SK_WARPS + warp) * SK_COLS;  // first output column of this warp
-    if (c0 >= n_out) return;
-    // weight rows this warp reads: for EPI 1 column c needs gate row c and up row n_out + c
-    constexpr int WR = EPI == 1 ? 2 * SK_COLS : SK_COLS;
-    const __nv_bfloat16* wrow[WR];
-#pragma unroll
-    for (int c = 0; c < SK_COLS; ++c) {
-        int col = min(c0 + c, n_out - 1);
-        wrow[c] = w + (size_t)col * K;
-        if (EPI == 1) wrow[SK_COLS + c] = w + (size_t)(n_out + col) * K;
+    // weight rows of this block's m16 tile: rows 0-7 and 8-15
+    int row_lo, row_hi;
+    if (EPI == 1) {
+        int c = blockIdx.x * 8 + g;
+        row_lo = min(c, n_out - 1);
+        row_hi = n_out + row_lo;
+    } else {
+        row_lo = min(blockIdx.x * 16 + g, N - 1);
+        row_hi = min(blockIdx.x * 16 + g + 8, N - 1);
     }
-    float acc[WR][SK_ROWS];
+    const __nv_bfloat16* wa = w + (size_t)row_lo * K;
+    const __nv_bfloat16* wb = w + (size_t)row_hi * K;
+    const __nv_bfloat16* xr[NT];
+    bool xok[NT];
 #pragma unroll
-    for (int c = 0; c < WR; ++c)
+    for (int t = 0; t < NT; ++t) {
+        int m = t * 8 + g;
+        xok[t] = m < M;
+        xr[t] = x + (size_t)(xok[t] ? m : 0) * K;
+    }
+    float acc[NT][4];
 #pragma unroll
-        for (int r = 0; r < SK_ROWS; ++r) acc[c][r] = 0.f;
+    for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
 
-    const int kvec = (K / 8) * 8;
-    for (int k = lane * 8; k < kvec; k += 32 * 8) {
-        bf16x8 wv[WR];
+    const int nblocks_all = (K + 31) / 32;
+    const int per_split = (nblocks_all + ksplits - 1) / ksplits;
+    const int kb_begin = blockIdx.y * per_split, nblocks = min(nblocks_all, kb_begin + per_split);
+    for (int kb0 = kb_begin + warp * SM_UNROLL; kb0 < nblocks; kb0 += SM_WARPS * SM_UNROLL) {
+        uint4 va[SM_UNROLL], vb[SM_UNROLL], vx[SM_UNROLL][NT];
 #pragma unroll
-        for (int c = 0; c < WR; ++c) wv[c] = *reinterpret_cast<const bf16x8*>(wrow[c] + k);
+        for (int u = 0; u < SM_UNROLL; ++u) {
+            int k = (kb0 + u) * 32 + tig * 8;
+            bool ok = kb0 + u < nblocks && k < K;  // K is a multiple of 8: a 16-byte chunk is all inside or all outside
+            va[u] = ok ? ldg_stream(wa + k) : make_uint4(0u, 0u, 0u, 0u);
+            vb[u] = ok ? ldg_stream(wb + k) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-        for (int r = 0; r < SK_ROWS; ++r) {
-            if (r < rows) {
-                bf16x8 xv = *reinterpret_cast<const bf16x8*>(x + (size_t)(m0 + r) * K + k);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    float2 xf = __bfloat1622float2(xv.v[i]);
-#pragma unroll
-                    for (int c = 0; c < WR; ++c) {
-                        float2 wf = __bfloat1622float2(wv[c].v[i]);
-                        acc[c][r] = fmaf(xf.x, wf.x, acc[c][r]);
-                        acc[c][r] = fmaf(xf.y, wf.y, acc[c][r]);
-                    }
-                }
-            }
+            for (int t = 0; t < NT; ++t)
+                vx[u][t] = (ok && xok[t]) ? *reinterpret_cast<const uint4*>(xr[t] + k) : make_uint4(0u, 0u, 0u, 0u);
         }
-    }
-    for (int k = kvec + lane; k < K; k += 32) {  // K not a multiple of 8
 #pragma unroll
-        for (int r = 0; r < SK_ROWS; ++r)
-            if (r < rows) {
-                float xf = __bfloat162float(x[(size_t)(m0 + r) * K + k]);
+        for (int u = 0; u < SM_UNROLL; ++u)
 #pragma unroll
-                for (int c = 0; c < WR; ++c) acc[c][r] = fmaf(xf, __bfloat162float(wrow[c][k]), acc[c][r]);
+            for (int t = 0; t < NT; ++t) {
+                mma16816(acc[t], va[u].x, vb[u].x, va[u].y, vb[u].y, vx[u][t].x, vx[u][t].y);
+                mma16816(acc[t], va[u].z, vb[u].z, va[u].w, vb[u].w, vx[u][t].z, vx[u][t].w);
             }
     }
 #pragma unroll
-    for (int c = 0; c < WR; ++c)
+    for (int t = 0; t < NT; ++t) {
+        red[warp][g][t * 8 + tig * 2] = acc[t][0];
+        red[warp][g][t * 8 + tig * 2 + 1] = acc[t][1];
+        red[warp][g + 8][t * 8 + tig * 2] = acc[t][2];
+        red[warp][g + 8][t * 8 + tig * 2 + 1] = acc[t][3];
+    }
+    __syncthreads();
+    const int out_rows = EPI == 1 ? 8 : 16;
+    if (ksplits > 1) {
+        for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += SM_WARPS * 32) {
+            int r = idx / (NT * 8), m = idx % (NT * 8);
+            float v = 0.f;
 #pragma unroll
-        for (int r = 0; r < SK_ROWS; ++r) acc[c][r] = warp_sum(acc[c][r]);
-    if (lane == 0) {
-#pragma unroll
-        for (int c = 0; c < SK_COLS; ++c) {
-            int col = c0 + c;
-            if (col >= n_out) break;
-#pragma unroll
-            for (int r = 0; r < SK_ROWS; ++r) {
-                if (r >= rows) break;
-                float v = acc[c][r];
-                if (EPI == 1) {
-                    // the gate and up products are rounded to bfloat16 first, as separate
-                    // GEMMs with bfloat16 outputs would leave them
-                    float g = __bfloat162float(__float2bfloat16_rn(v));
-                    float u = __bfloat162float(__float2bfloat16_rn(acc[SK_COLS + c][r]));
-                    v = g / (1.f + expf(-g)) * u;
-                }
-                y[(size_t)(m0 + r) * n_out + col] = from_float<TO>(v);
+            for (int wi = 0; wi < SM_WARPS; ++wi) v += red[wi][r][m];
+            part[r][m] = v;
+        }
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();  // every block's partial sums are written
+        if (blockIdx.y == 0) {
+            for (int idx = threadIdx.x; idx < 16 * NT * 8; idx += SM_WARPS * 32) {
+                int r = idx / (NT * 8), m = idx % (NT * 8);
+                float v = part[r][m];
+                for (int rank = 1; rank < ksplits; ++rank)
+                    v += cluster.map_shared_rank(&part[0][0], rank)[r * (NT * 8) + m];
+                red[0][r][m] = v;
             }
         }
+        cluster.sync();  // nobody leaves while its shared memory may still be read
+        if (blockIdx.y != 0) return;
+        __syncthreads();
+    }
+    for (int idx = threadIdx.x; idx < out_rows * NT * 8; idx += SM_WARPS * 32) {
+        int m = idx / out_rows, r = idx % out_rows;  // consecutive threads write consecutive columns
+        int col = blockIdx.x * out_rows + r;
+        if (m >= M || col >= n_out) continue;
+        float v = 0.f, u = 0.f;
+        if (ksplits > 1) {
+            v = red[0][r][m];
+            if (EPI == 1) u = red[0][r + 8][m];
+        } else {
+#pragma unroll
+            for (int wi = 0; wi < SM_WARPS; ++wi) {
+                v += red[wi][r][m];
+                if (EPI == 1) u += red[wi][r + 8][m];
+            }
+        }
+        if (EPI == 1) v = v / (1.f + expf(-v)) * u;
+        y[(size_t)m * n_out + col] = from_float<TO>(v);
     }
 }
 
-// x, w: bfloat16; K-rows of x and w must start 16-byte aligned when K % 8 == 0 is used
-// for vector loads (K % 8 != 0 falls to scalar loads for the tail only if rows stay aligned).
+// x [M, K] and w [N, K] bfloat16, rows 16-byte aligned (K % 8 == 0); M <= 16.
 extern "C" int linear_skinny(const void* x, const void* w, void* y, int out_dtype, int epilogue, const int* meta,
                              int use_rows, int M, int N, int K, cudaStream_t stream) {
+    (void)meta; (void)use_rows;  // padded rows are computed too: they are rows of the same buffers
     if (M <= 0 || N <= 0) return 0;
-    if (K % 8 != 0) return (int)cudaErrorInvalidValue;  // rows would lose 16-byte alignment
-    if (epilogue == 1 && (N % 2)) return (int)cudaErrorInvalidValue;
-    int n_out = epilogue == 1 ? N / 2 : N;
-    dim3 grid((n_out + SK_WARPS * SK_COLS - 1) / (SK_WARPS * SK_COLS), (M + SK_ROWS - 1) / SK_ROWS);
+    if (K % 8 != 0 || M > SM_MAX_ROWS) return (int)cudaErrorInvalidValue;
+    if (epilogue == 1 && ((N % 2) || out_dtype != DT_BF16)) return (int)cudaErrorInvalidValue;
     const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
     const __nv_bfloat16* wb = (const __nv_bfloat16*)w;
+    const int n_out = epilogue == 1 ? N / 2 : N;
+    const int tiles = epilogue == 1 ? (n_out + 7) / 8 : (N + 15) / 16;
+    // Too few tiles to fill the GPU: clusters of blocks split K (at least one 32-wide k block per warp each).
+    int sms = 148;
+    int ksplits = (2 * sms + tiles - 1) / tiles;
+    ksplits = max(1, min(min(ksplits, 8), ((K + 31) / 32) / SM_WARPS));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles, ksplits, 1);
+    cfg.blockDim = dim3(SM_WARPS * 32, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = ksplits;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ksplits > 1 ? 1 : 0;  // a plain launch when no cluster is needed
+    cudaError_t err;
+#define SMALL(TO, NT, EPI) err = cudaLaunchKernelEx(&cfg, linear_small_kernel<TO, NT, EPI>, xb, wb, (TO*)y, M, N, K, ksplits)
     if (epilogue == 1) {
-        if (out_dtype != DT_BF16) return (int)cudaErrorInvalidValue;
-        linear_skinny_kernel<__nv_bfloat16, 1><<<grid, SK_WARPS * 32, 0, stream>>>(xb, wb, (__nv_bfloat16*)y, meta, use_rows, M, N, K);
+        if (M <= 8) SMALL(__nv_bfloat16, 1, 1); else SMALL(__nv_bfloat16, 2, 1);
     } else if (out_dtype == DT_F32) {
-        linear_skinny_kernel<float, 0><<<grid, SK_WARPS * 32, 0, stream>>>(xb, wb, (float*)y, meta, use_rows, M, N, K);
+        if (M <= 8) SMALL(float, 1, 0); else SMALL(float, 2, 0);
     } else {
-        linear_skinny_kernel<__nv_bfloat16, 0><<<grid, SK_WARPS * 32, 0, stream>>>(xb, wb, (__nv_bfloat16*)y, meta, use_rows, M, N, K);
+        if (M <= 8) SMALL(__nv_bfloat16, 1, 0); else SMALL(__nv_bfloat16, 2, 0);
     }
+#undef SMALL
+    if (err != cudaSuccess) return (int)err;
     LAUNCH_RETURN();
 }

@@ -144,14 +144,15 @@ class CudaOps:
                 scratch = torch.empty(n, dtype=torch.float32, device=q.device) if n else None
                 self._check(lib.attn_decode(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
                                             _p(ctx.positions), _p(out), _p(scratch), S, nq, nkv, page_size, num_pages,
-                                            window, ctypes.c_float(scale), splits, _p(self.status), self._stream()),
+                                            window, ctypes.c_float(scale), splits, ctx.max_context, _p(self.status),
+                                            self._stream()),
                             "attn_decode")
                 self.launches += int(splits > 1)
             else:
                 self._check(lib.attn_prefill(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
                                              _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
-                                             page_size, num_pages, window, ctypes.c_float(scale), _p(self.status),
-                                             self._stream()), "attn_prefill")
+                                             page_size, num_pages, window, ctypes.c_float(scale), ctx.max_context,
+                                             _p(self.status), self._stream()), "attn_prefill")
             return
         if d > 256:
             raise KernelError(f"head size {d} is not supported (at most 256)")

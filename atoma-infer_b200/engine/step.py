@@ -211,14 +211,17 @@ class StepFunction:
             else:
                 torch.cuda.synchronize(self.rt.device)
                 graph = torch.cuda.CUDAGraph()
+                before = self.rt.ops.launches
                 with torch.cuda.graph(graph):
                     g.logits = self.model.forward(ctx, self.cache, rows, bucket)
+                g.kernels = self.rt.ops.launches - before  # own kernels in one replay
                 g.graph = graph
                 graph.replay()
                 logits = g.logits
         else:
             g.graph.replay()
             self.graph_replays += 1
+            self.rt.ops.launches += g.kernels
             logits = g.logits
         for i in infos:
             self.manager.advance(i.req, i.num_tokens)
@@ -239,3 +242,4 @@ class _DecodeGraph:
         self.graph = None
         self.logits = None
         self.warm = False
+        self.kernels = 0
