@@ -53,13 +53,24 @@ def _digest(paths: Sequence[str], extra: str) -> str:
     return h.hexdigest()[:16]
 
 
-def _headers() -> Sequence[str]:
-    out = []
-    for root, _dirs, files in os.walk(CSRC):
-        if os.path.basename(root) == "_build":
+def _with_includes(paths: Sequence[str]) -> Sequence[str]:
+    """The sources and every file they include with quotes, transitively (for the cache key)."""
+    import re
+
+    seen, todo = [], list(paths)
+    while todo:
+        p = todo.pop()
+        if p in seen or not os.path.isfile(p):
             continue
-        out += [os.path.join(root, f) for f in files if f.endswith((".cuh", ".hpp", ".h"))]
-    return sorted(out)
+        seen.append(p)
+        with open(p, errors="replace") as f:
+            for inc in re.findall(r'^\s*#\s*include\s+"([^"]+)"', f.read(), flags=re.M):
+                for base in (os.path.dirname(p), CSRC):
+                    q = os.path.normpath(os.path.join(base, inc))
+                    if os.path.isfile(q):
+                        todo.append(q)
+                        break
+    return sorted(seen)
 
 
 def _run(cmd: Sequence[str], what: str) -> None:
@@ -84,7 +95,7 @@ def build_library(name: str, sources: Sequence[str], *, cuda: bool, defines: Opt
     srcs = [os.path.join(CSRC, s) for s in sources]
     defs = [f"-D{k}={v}" for k, v in sorted((defines or {}).items())]
     flags = (NVCC_FLAGS + ARCH_FLAGS if cuda else GXX_FLAGS) + list(extra_flags) + defs
-    tag = _digest(srcs + list(_headers()), " ".join(flags))
+    tag = _digest(list(_with_includes(srcs)), " ".join(flags))
     os.makedirs(BUILD_DIR, exist_ok=True)
     out = os.path.join(BUILD_DIR, f"{name}-{tag}.so")
     if os.path.isfile(out):
@@ -127,4 +138,5 @@ def all_kernel_libraries():
     from .ops import ATTENTION_HEAD_DIMS, ATTENTION_SOURCES, CORE_SOURCES
 
     return [("core", CORE_SOURCES, None)] + [
-        (f"attention_d{d}", ATTENTION_SOURCES, {"HEAD_DIM": d}) for d in ATTENTION_HEAD_DIMS]
+        (f"attention_d{d}", ATTENTION_SOURCES, {"HEAD_DIM": d}) for d in ATTENTION_HEAD_DIMS] + [
+        ("attention_noalloc_d64", ["kernels/attention_noalloc.cu"], {"HEAD_DIM": 64})]
