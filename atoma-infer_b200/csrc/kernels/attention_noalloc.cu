@@ -1,0 +1,63 @@
+// attn_decode_noalloc: see attention_noalloc.h for what it is for and what it promises.
+//
+// The kernels are those of attention_bf16.cu, compiled into this library as well
+// (same -DHEAD_DIM); only the home of the split scratch differs.
+#include <cstdio>
+
+#include "attention_bf16.cu"
+#include "attention_noalloc.h"
+
+// The scratch itself.  In host code this name is only a handle for the runtime's
+// symbol calls, not an address a kernel could use: the device address comes from
+// cudaGetSymbolAddress below, once per device.
+static __device__ __align__(256) float g_noalloc_scratch[ATTN_NOALLOC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_scratch_ptr[kMaxDevices] = {};  // device address of the array, per device ordinal
+
+int fail(int code, char* err, int cap, const char* msg) {
+    if (err && cap > 0) snprintf(err, (size_t)cap, "%s", msg);
+    return code;
+}
+}  // namespace
+
+extern "C" int attn_decode_noalloc(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                   const int* cu_tokens, const int* positions, void* out, int S, int nq, int nkv,
+                                   int page_size, int num_pages, int window, float scale, int splits, int max_context,
+                                   int* status, cudaStream_t stream, char* err, int err_cap) {
+    char msg[256];
+    if (S <= 0 || nq <= 0 || nkv <= 0 || splits < 1 || page_size <= 0)
+        return fail(ATTN_NOALLOC_BAD_ARGUMENT, err, err_cap, "attn_decode_noalloc: S, heads, splits and page_size must be positive");
+    const size_t need = attn_decode_scratch_floats(S, nq, splits);
+    if (need > (size_t)ATTN_NOALLOC_SCRATCH_FLOATS) {
+        snprintf(msg, sizeof msg,
+                 "attn_decode_noalloc: %d requests x %d heads x %d splits x (%d + 2) = %zu floats of scratch, the built-in "
+                 "array holds %u; use fewer splits or requests per call, or attn_decode with a buffer of your own",
+                 S, nq, splits, D, need, ATTN_NOALLOC_SCRATCH_FLOATS);
+        return fail(ATTN_NOALLOC_TOO_LARGE, err, err_cap, msg);
+    }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        snprintf(msg, sizeof msg, "attn_decode_noalloc: no usable current device (%s)", cudaGetErrorString(e));
+        return fail(e != cudaSuccess ? (int)e : ATTN_NOALLOC_BAD_ARGUMENT, err, err_cap, msg);
+    }
+    if (!g_scratch_ptr[dev]) {  // first call on this device, with it current
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            snprintf(msg, sizeof msg, "attn_decode_noalloc: cudaGetSymbolAddress failed on device %d (%s)", dev,
+                     cudaGetErrorString(e));
+            return fail(e != cudaSuccess ? (int)e : ATTN_NOALLOC_BAD_ARGUMENT, err, err_cap, msg);
+        }
+        g_scratch_ptr[dev] = p;
+    }
+    int rc = attn_decode(q, q_stride, cache, meta, group, cu_tokens, positions, out, g_scratch_ptr[dev], S, nq, nkv,
+                         page_size, num_pages, window, scale, splits, max_context, status, stream);
+    if (rc != 0) {
+        snprintf(msg, sizeof msg, "attn_decode_noalloc: launch failed (%s)", cudaGetErrorString((cudaError_t)rc));
+        return fail(rc, err, err_cap, msg);
+    }
+    return 0;
+}
