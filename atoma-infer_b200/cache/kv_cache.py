@@ -1,7 +1,8 @@
 """Device memory of the cache: pages of keys and values per group, state slots per layer.
 
 One tensor per cache group, ``[layers_in_group, num_pages, 2, kv_heads, page_size,
-head_dim]``: a page id addresses the same page in every layer of its group, and the
+head_dim]``: a page id addresses the same page in every layer of its group (a layer here is
+a run of the model's schedule that owns a cache), and the
 (page, K|V, head) block of page_size * head_dim elements is contiguous.  The
 reference keeps ``[2, num_blocks, block_size, kv_heads, head_dim]`` per layer
 (backends/vllm/src/worker.rs:592-595, models/src/flash_attention.rs:239-246); the
@@ -41,14 +42,15 @@ class KVCache:
             # Poison: a key or value that is read without having been written shows as NaN.
             t.fill_(float("nan")) if poison else t.zero_()
             self.pages.append(t)
-        self.state: Dict[int, torch.Tensor] = {
-            layer: torch.zeros((max_seqs, nbytes), dtype=torch.uint8, device=rt.device)
-            for layer, nbytes in enumerate(model.state_bytes) if nbytes
+        self.state: Dict[int, torch.Tensor] = {  # by run of the model's schedule
+            run: torch.zeros((max_seqs, nbytes), dtype=torch.uint8, device=rt.device)
+            for run, nbytes in enumerate(model.state_bytes) if nbytes
         }
 
-    def layer_view(self, owner: int, writes: bool = True, state_layer: Optional[int] = None) -> LayerCache:
-        state = self.state.get(owner if state_layer is None else state_layer)
-        where = self.model.layer_group.get(owner)
+    def layer_view(self, owner: int, writes: bool = True, state_run: Optional[int] = None) -> LayerCache:
+        """What a run sees: the pages of the run that owns its cache, and its own state."""
+        state = self.state.get(owner if state_run is None else state_run)
+        where = self.model.run_group.get(owner)
         if where is None:
             return LayerCache(group=-1, page_size=self.page_size, writes=False, state=state)
         gi, idx = where

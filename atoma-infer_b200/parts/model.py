@@ -77,22 +77,30 @@ class DecoderModel:
         self.blocks = _build_layers(spec)
         self.final_norm = part_class("norm", spec.final_norm["kind"])(spec.final_norm, spec.final_norm_prefix)
         self.runs = spec.runs()
-        for r in self.runs:
+        # Who owns which cache: a run without ``cache_of`` owns pages (and state) of its own, so a layer
+        # that runs twice keeps two caches; a run with ``cache_of`` reads the pages of the first owning
+        # run of that layer, which must come earlier in the schedule (its keys of this step are written).
+        self.run_owner: List[int] = []
+        first_owner: Dict[int, int] = {}
+        for i, r in enumerate(self.runs):
             if not (0 <= r.layer < len(self.blocks)):
                 raise ValueError(f"schedule names layer {r.layer}, the model has {len(self.blocks)}")
-            owner = r.layer if r.cache_of is None else r.cache_of
-            if not (0 <= owner < len(self.blocks)):
-                raise ValueError(f"schedule lets layer {r.layer} read the cache of layer {owner}, which does not exist")
-            a, b = self.blocks[r.layer].mixer.cache_need(), self.blocks[owner].mixer.cache_need()
+            if r.cache_of is None:
+                first_owner.setdefault(r.layer, i)
+                self.run_owner.append(i)
+                continue
+            if r.cache_of not in first_owner:
+                raise ValueError(f"schedule lets layer {r.layer} read the cache of layer {r.cache_of}, "
+                                 f"which has not run (with a cache of its own) before it")
+            a, b = self.blocks[r.layer].mixer.cache_need(), self.blocks[r.cache_of].mixer.cache_need()
             if a != b:
-                raise ValueError(f"layer {r.layer} cannot read the cache of layer {owner}: {a} != {b}")
-        # Cache groups: layers that own a cache, put together by what they need.  A layer
-        # owns a cache if some run uses it as its cache layer.
-        owners = sorted({(r.layer if r.cache_of is None else r.cache_of) for r in self.runs})
+                raise ValueError(f"layer {r.layer} cannot read the cache of layer {r.cache_of}: {a} != {b}")
+            self.run_owner.append(first_owner[r.cache_of])
+        # Cache groups: owning runs put together by what they need.
         self.groups: List[CacheGroup] = []
-        self.layer_group: Dict[int, Tuple[int, int]] = {}  # layer -> (group, index within the group)
-        for layer in owners:
-            need = self.blocks[layer].mixer.cache_need()
+        self.run_group: Dict[int, Tuple[int, int]] = {}  # owning run -> (group, index within the group)
+        for i in sorted(set(self.run_owner)):
+            need = self.blocks[self.runs[i].layer].mixer.cache_need()
             if need is None:
                 continue
             for gi, g in enumerate(self.groups):
@@ -101,9 +109,10 @@ class DecoderModel:
             else:
                 self.groups.append(CacheGroup(need))
                 gi = len(self.groups) - 1
-            self.layer_group[layer] = (gi, len(self.groups[gi].layers))
-            self.groups[gi].layers.append(layer)
-        self.state_bytes = [blk.mixer.state_bytes() for blk in self.blocks]
+            self.run_group[i] = (gi, len(self.groups[gi].layers))
+            self.groups[gi].layers.append(i)
+        # fixed-size state per request, for every run of a mixer that has some
+        self.state_bytes = [self.blocks[r.layer].mixer.state_bytes() for r in self.runs]
         # a step of this model can be captured in a CUDA graph if no part reads the host-side entry list
         self.graph_safe = all(getattr(blk.mixer, "graph_safe", False) for blk in self.blocks)
 
@@ -126,10 +135,9 @@ class DecoderModel:
         resid = torch.empty((ctx.T, self.spec.hidden_size), dtype=torch.float32, device=self.rt.device)
         ops.embed(ctx.tokens, self.embedding, resid, ctx.meta, ctx.T)
         delta = None
-        for run in self.runs:
-            owner = run.layer if run.cache_of is None else run.cache_of
-            delta = self.blocks[run.layer].forward(resid, delta, ctx, cache.layer_view(owner, writes=run.cache_of is None,
-                                                                                        state_layer=run.layer))
+        for i, run in enumerate(self.runs):
+            view = cache.layer_view(self.run_owner[i], writes=run.cache_of is None, state_run=i)
+            delta = self.blocks[run.layer].forward(resid, delta, ctx, view)
         if num_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
         h = self.final_norm.forward(resid, delta, ctx, rows=rows, num_rows=num_rows)

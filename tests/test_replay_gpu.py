@@ -43,3 +43,31 @@ def test_every_cutting_matches_plain(name, dtype, tiny_models, references, tmp_p
         assert worst <= tol, f"family {tag!r}: error {worst:.3g} of the logit scale at (step, request, position) {where}"
         if dtype == "float32":
             assert agree == 1.0, f"family {tag!r}: greedy tokens differ from the plain implementation"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_one_token_at_a_time(dtype, tiny_models, tmp_path):
+    """A short prompt and hundreds of single-token steps (the captured decode graph, many page edges)."""
+    d, cfg, page = tiny_models["B"]
+    seq = helpers.random_tokens(cfg["vocab_size"], (420,), seed=11)
+    ref = {k: P.forward(helpers.read_weights(d), cfg, v) for k, v in seq.items()}
+    steps = helpers.trace_tail(seq, tail=412)
+    steps, out = helpers.run_trace(d, dtype, steps, str(tmp_path), 448, page)
+    worst, where, agree = helpers.compare_trace(steps, out, cfg["vocab_size"], ref)
+    assert worst <= (helpers.FP32_TOL if dtype == "float32" else helpers.BF16_TOL), (worst, where)
+    assert agree == 1.0 if dtype == "float32" else agree > 0.97
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_first_tokens_of_sequences(name, dtype, tiny_models, tmp_path):
+    """Requests of one, two and three tokens: alone, together in one step, and token by token."""
+    d, cfg, page = tiny_models[name]
+    seqs = helpers.random_tokens(cfg["vocab_size"], (1, 2, 3, 1), seed=12)
+    ref = {k: P.forward(helpers.read_weights(d), cfg, v) for k, v in seqs.items()}
+    together = [{"entries": [{"id": f"g{k}", "tokens": v, "want": list(range(len(v)))} for k, v in seqs.items()],
+                 "end": [f"g{k}" for k in seqs]}]
+    steps = helpers.trace_whole(seqs, tag="w") + together + helpers.trace_tail(seqs, tail=3, tag="t")
+    steps, out = helpers.run_trace(d, dtype, steps, str(tmp_path), 256, page)
+    worst, where, agree = helpers.compare_trace(steps, out, cfg["vocab_size"], ref)
+    assert worst <= (helpers.FP32_TOL if dtype == "float32" else helpers.BF16_TOL), (worst, where)

@@ -1,0 +1,165 @@
+"""Generality of the parts layer, shown with toy parts that live in this test only: a mixer with
+per-request state of its own (no pages), an architecture whose layers differ (attention, toy
+mixer, attention that reads another layer's cache, a layer that runs twice), registered, written as
+a random model folder, loaded and stepped without any change to the framework's files."""
+import json
+import math
+
+import pytest
+import torch
+
+import helpers
+import plain_llama as P
+from atoma_infer_b200.config import register_architecture, register_part
+from atoma_infer_b200.parts import LayerRun, LayerSpec, Mixer, ModelSpec
+from atoma_infer_b200.weights import TensorDecl
+
+pytestmark = pytest.mark.gpu
+
+H, V = 48, 97
+
+
+class RunningMeanMixer(Mixer):
+    """out[t] = W * mean(x[0..t]) over the request's tokens so far.  Its state (running sum and
+    count) is fixed-size per request and lives in the engine's state slots; it keeps no pages."""
+
+    graph_safe = False  # walks the host-side entry list
+
+    def __init__(self, params, prefix):
+        super().__init__(params, prefix)
+        self.hidden = int(params["hidden"])
+
+    def state_bytes(self):
+        return 4 * (self.hidden + 1)
+
+    def declare(self):
+        return [TensorDecl(self.prefix + ".mix.weight", (self.hidden, self.hidden))]
+
+    def bind(self, tensors, rt):
+        super().bind(tensors, rt)
+        self.w = tensors[self.prefix + ".mix.weight"].float()
+
+    def forward(self, x, ctx, cache):
+        out = torch.empty_like(x)
+        state = cache.state.view(torch.float32)  # [slots, hidden + 1]
+        for e in ctx.entries:
+            rows = slice(e.start, e.start + e.num_tokens)
+            s = state[e.state_slot]
+            sums = s[:self.hidden] + torch.cumsum(x[rows].float(), 0)
+            counts = s[self.hidden] + torch.arange(1, e.num_tokens + 1, device=x.device, dtype=torch.float32)
+            out[rows] = ((sums / counts[:, None]) @ self.w.T).to(x.dtype)
+            s[:self.hidden] = sums[-1]
+            s[self.hidden] = counts[-1]
+        return out
+
+
+def toy_config(raw):
+    return dict(raw)
+
+
+def toy_spec(cfg):
+    norm = {"kind": "rmsnorm", "size": H, "eps": cfg["eps"]}
+    attn = {"kind": "attention", "hidden": H, "num_heads": 3, "num_kv_heads": 1, "head_dim": 16,
+            "scale": 0.25, "window": None, "position": {"kind": "rope", "head_dim": 16, "theta": 100.0}}
+    windowed = dict(attn, window=cfg["window"], num_kv_heads=3)
+    ff = {"kind": "swiglu", "hidden": H, "intermediate": 80}
+    mean = {"kind": "toy_running_mean", "hidden": H}
+    blocks = [attn, mean, attn, windowed]
+    names = [None, {"mixer": "mean"}, None, None]
+    layers = [LayerSpec(f"model.layers.{i}", {"kind": "prenorm", "norm": norm, "mixer": m, "feed_forward": ff,
+                                               **({"names": n} if n else {})})
+              for i, (m, n) in enumerate(zip(blocks, names))]
+    # layer 2 keeps no keys of its own: it reads layer 0's; layer 1 (the toy mixer) runs twice
+    schedule = [LayerRun(0), LayerRun(1), LayerRun(2, cache_of=0), LayerRun(3), LayerRun(1)]
+    return ModelSpec(hidden_size=H, vocab_size=V, layers=layers, final_norm=norm, head_tensor="lm_head.weight",
+                     schedule=schedule, max_position=512)
+
+
+@pytest.fixture(scope="module")
+def toy_model(tmp_path_factory):
+    register_part("mixer", "toy_running_mean", RunningMeanMixer, replace=True)
+    register_architecture("ToyForCausalLM", toy_config, toy_spec, replace=True)
+    d = str(tmp_path_factory.mktemp("toy"))
+    cfg = {"architectures": ["ToyForCausalLM"], "eps": 1e-5, "window": 7}
+    helpers.make_model(d, cfg, seed=4, std=0.2)
+    return d, cfg
+
+
+def plain_toy(w, cfg, tokens):
+    """The same model, whole sequence, float64, no cache, no state."""
+    w = {k: v.double() for k, v in w.items()}
+    T = len(tokens)
+    pos = torch.arange(T)
+    x = w["model.embed_tokens.weight"][torch.as_tensor(tokens)]
+    inv = 1.0 / torch.pow(torch.tensor(100.0), torch.arange(0, 16, 2, dtype=torch.float32) / 16)
+
+    def attention(h, p, nkv, window, kv_from=None):
+        q = (h @ w[p + "q_proj.weight"].T).reshape(T, 3, 16)
+        src = kv_from if kv_from is not None else h
+        sp = kv_from_prefix if kv_from is not None else p
+        k = (src @ w[sp + "k_proj.weight"].T).reshape(T, nkv, 16)
+        v = (src @ w[sp + "v_proj.weight"].T).reshape(T, nkv, 16)
+        o = P.causal_attention(P.rope(q, pos, inv), P.rope(k, pos, inv), v, 0.25, window)
+        return o.reshape(T, 48) @ w[p + "o_proj.weight"].T
+
+    def mean_mixer(h, p):
+        return (torch.cumsum(h, 0) / torch.arange(1, T + 1)[:, None]) @ w[p + "mix.weight"].T
+
+    def block(x, i, mix):
+        p = f"model.layers.{i}."
+        h = x + mix(P.rms_norm(x, w[p + "input_layernorm.weight"], cfg["eps"]))
+        return h + P.swiglu(P.rms_norm(h, w[p + "post_attention_layernorm.weight"], cfg["eps"]), w, p + "mlp.")
+
+    normed0 = P.rms_norm(x, w["model.layers.0.input_layernorm.weight"], cfg["eps"])  # what layer 0's keys are made from
+    kv_from_prefix = "model.layers.0.self_attn."
+    x = block(x, 0, lambda h: attention(h, "model.layers.0.self_attn.", 1, None))
+    x = block(x, 1, lambda h: mean_mixer(h, "model.layers.1.mean."))
+    x = block(x, 2, lambda h: attention(h, "model.layers.2.self_attn.", 1, None, kv_from=normed0))
+    x = block(x, 3, lambda h: attention(h, "model.layers.3.self_attn.", 3, cfg["window"]))
+    x = block(x, 1, lambda h: mean_mixer(h, "model.layers.1.mean."))
+    return P.rms_norm(x, w["model.norm.weight"], cfg["eps"]) @ w["lm_head.weight"].T
+
+
+def test_toy_architecture_is_built_and_stepped_without_touching_the_framework(toy_model):
+    from atoma_infer_b200.engine import StepEntry, load_model
+
+    d, cfg = toy_model
+    lm = load_model(d, dtype="float32", device="cuda:0", page_size=4, num_pages=40, max_seqs=3, poison_cache=True)
+    model = lm.model
+    # the cache plan follows the spec: layers 0 and 3 own pages (two groups: all keys / a window),
+    # layer 2 owns none, layer 1 has state and no pages
+    assert [g.layers for g in model.groups] == [[0], [3]] and model.groups[1].need.window == 7
+    assert model.state_bytes == [0, 4 * (H + 1), 0, 0, 4 * (H + 1)] and not model.graph_safe  # per run
+    w = helpers.read_weights(d)
+    seqs = helpers.random_tokens(V, (23, 9, 31), seed=8)
+    ref = {k: plain_toy(w, cfg, v) for k, v in seqs.items()}
+    # mixed steps: portions of changing size, requests beside one another, one request after another in a slot
+    pos = {k: 0 for k in seqs}
+    live, pending, sizes, si = ["r0", "r1"], ["r2"], (5, 1, 3, 2, 7), 0
+    ids = {k: i for i, k in enumerate(seqs)}
+    worst = 0.0
+    while live:
+        entries, meta = [], []
+        for k in list(live):
+            n = min(sizes[si % len(sizes)], len(seqs[k]) - pos[k])
+            si += 1
+            entries.append(StepEntry(ids[k], seqs[k][pos[k]:pos[k] + n], list(range(n))))
+            meta.append((k, pos[k], n))
+            pos[k] += n
+        logits = lm.step.run(entries).double().cpu()
+        lm.rt.ops.check_status()
+        row = 0
+        for k, start, n in meta:
+            scale = float(ref[k].abs().max())
+            worst = max(worst, float((logits[row:row + n] - ref[k][start:start + n]).abs().max()) / scale)
+            row += n
+            if pos[k] == len(seqs[k]):
+                lm.step.finish(ids[k])
+                live.remove(k)
+                if pending:
+                    live.append(pending.pop())  # takes the freed state slot and pages
+        assert lm.manager.audit() == ""
+    assert worst < 5e-5, worst
+    # the windowed group gave pages back while requests ran; in the end nothing is held
+    assert lm.manager.num_requests() == 0
+    assert all(lm.manager.num_free_pages(g) == 40 for g in range(2)) and lm.manager.num_free_slots() == 3
