@@ -23,18 +23,31 @@
 #ifndef HEAD_DIM
 #define HEAD_DIM 64
 #endif
+int g_use_pdl = 1;
+extern "C" void kernels_set_pdl(int on) { g_use_pdl = on ? 1 : 0; }
+
 static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head sizes 16..256 in steps of 16");
 
 namespace {
 
 constexpr int D = HEAD_DIM;
-constexpr int LDS = D + 8;            // padded row: consecutive rows shift by 16 bytes, ldmatrix stays conflict-free
+// Tiles are [rows][LDS].  Head sizes that are multiples of 64 use dense rows whose 16-byte chunks are
+// XOR-swizzled by the row (chunk ^ (row & 7)); other head sizes pad each row by 16 bytes.  Either way
+// the eight rows an ldmatrix reads fall into different banks.
+constexpr bool SWZ = D % 64 == 0;
+constexpr int LDS = SWZ ? D : D + 8;
 constexpr int KSTEPS = D / 16;        // k-steps of Q*K^T
 constexpr int DTILES = D / 8;         // n-tiles of the output
 constexpr bool Q_IN_REGS = D <= 128;  // larger heads reload Q fragments from shared memory
 constexpr float LOG2E = 1.4426950408889634f;
 
 typedef __nv_bfloat16 bf16;
+
+// element offset of (row, col) in a tile; vector accesses pass a col that is a multiple of 8
+__device__ __forceinline__ int toff(int row, int col) {
+    if (SWZ) return row * D + ((((col >> 3) ^ (row & 7)) << 3) | (col & 7));
+    return row * LDS + col;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem) {
@@ -94,8 +107,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* ktile, bf16* vtile, const bf1
     for (int idx = tid; idx < rows * PAIRS; idx += nthreads) {
         int r = idx / PAIRS, c = (idx % PAIRS) * 16;
         int pos = k0 + r;
-        bf16* kd = ktile + r * LDS + c;
-        bf16* vd = vtile + r * LDS + c;
+        const int o0 = toff(r, c), o1 = toff(r, c + 8);
         int page = -1, slot = 0;
         if (pos >= lo && pos < hi) {
             int pidx = ps_shift >= 0 ? pos >> ps_shift : pos / ps;
@@ -104,16 +116,16 @@ __device__ __forceinline__ void load_kv_tile(bf16* ktile, bf16* vtile, const bf1
         }
         if (page > 0) {
             const bf16* src = cache + (size_t)page * page_stride + head_off + (size_t)slot * D + c;
-            cp_async_16(kd, src);
-            cp_async_16(kd + 8, src + 8);
-            cp_async_16(vd, src + v_off);
-            cp_async_16(vd + 8, src + v_off + 8);
+            cp_async_16(ktile + o0, src);
+            cp_async_16(ktile + o1, src + 8);
+            cp_async_16(vtile + o0, src + v_off);
+            cp_async_16(vtile + o1, src + v_off + 8);
         } else {
             uint4 z = make_uint4(0u, 0u, 0u, 0u);
-            *reinterpret_cast<uint4*>(kd) = z;
-            *reinterpret_cast<uint4*>(kd + 8) = z;
-            *reinterpret_cast<uint4*>(vd) = z;
-            *reinterpret_cast<uint4*>(vd + 8) = z;
+            *reinterpret_cast<uint4*>(ktile + o0) = z;
+            *reinterpret_cast<uint4*>(ktile + o1) = z;
+            *reinterpret_cast<uint4*>(vtile + o0) = z;
+            *reinterpret_cast<uint4*>(vtile + o1) = z;
         }
     }
 }
@@ -121,7 +133,7 @@ __device__ __forceinline__ void load_kv_tile(bf16* ktile, bf16* vtile, const bf1
 // A fragments (16 rows x 16 dims, k-step ks) of a row-major tile [16][LDS]
 __device__ __forceinline__ void load_a_frag(uint32_t (&a)[4], const bf16* tile16, int ks, int lane) {
     int row = (lane & 7) + ((lane >> 3) & 1) * 8, col = ks * 16 + (lane >> 4) * 8;
-    ldmatrix_x4(a, tile16 + row * LDS + col);
+    ldmatrix_x4(a, tile16 + toff(row, col));
 }
 
 // S[16 x NK*8] = Q (fragments) * K^T for NK n-tiles of keys starting at tile row 0
@@ -140,7 +152,7 @@ __device__ __forceinline__ void qk_tile(float (&s)[NK][4], const uint32_t (*qf)[
             uint32_t b[4];
             int j = lane >> 3;
             int key = np * 16 + (lane & 7) + (j >> 1) * 8, dim = ks * 16 + (j & 1) * 8;
-            ldmatrix_x4(b, ktile + key * LDS + dim);
+            ldmatrix_x4(b, ktile + toff(key, dim));
             mma_bf16(s[2 * np], a, b[0], b[1]);
             mma_bf16(s[2 * np + 1], a, b[2], b[3]);
         }
@@ -159,7 +171,7 @@ __device__ __forceinline__ void pv_tile(float (&o)[DTILES][4], const float (&s)[
             uint32_t b[4];
             int j = lane >> 3;
             int key = ks * 16 + (lane & 7) + (j & 1) * 8, dim = dp * 16 + (j >> 1) * 8;
-            ldmatrix_x4_trans(b, vtile + key * LDS + dim);
+            ldmatrix_x4_trans(b, vtile + toff(key, dim));
             mma_bf16(o[2 * dp], a, b[0], b[1]);
             mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
         }
@@ -212,45 +224,158 @@ constexpr size_t DEC_TILE_BYTES = (size_t)(16 * LDS + DEC_WARPS * DEC_WARP_ELEMS
 constexpr size_t DEC_MERGE_BYTES = (size_t)DEC_WARPS * (32 + 16 * D) * sizeof(float);
 constexpr size_t DEC_SMEM = 16 * LDS * sizeof(bf16) +
     (DEC_WARPS * DEC_WARP_ELEMS * sizeof(bf16) > DEC_MERGE_BYTES ? DEC_WARPS * DEC_WARP_ELEMS * sizeof(bf16) : DEC_MERGE_BYTES);
-// + a slice of the block table, sized by the host (bt_cap entries)
+constexpr int DEC_BLOCKS_PER_SM = (int)((227 * 1024) / (DEC_SMEM + 1024)) < 8 ? (int)((227 * 1024) / (DEC_SMEM + 1024)) : 8;
 }  // namespace
 
+// One block per (split, key/value head, request).  Optional fusions for decode steps:
+//  * inv_freq != null: the row of the fused projection is still unrotated; the kernel rotates the
+//    group's query heads itself and (store_kv) the block that owns the newest position rotates
+//    the new key, writes it and the new value to their page, and only then loads that tile;
+//  * splits > 1: every block leaves its partial result in scratch and counts itself in; the last
+//    block to arrive for a (request, head group) merges all splits in split order.  No block
+//    waits for another: whoever comes last does the merge.  `counters` must be zero before
+//    the launch and is zero again after it.
+// Before the dependency wait the kernel only touches what no kernel of the step writes: the
+// step's metadata (block table, positions) and keys and values of earlier steps.
 __global__ void __launch_bounds__(DEC_WARPS * 32)
-attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ cache, CacheLayout L,
+attn_decode_kernel(bf16* __restrict__ q, int q_stride, bf16* __restrict__ cache, CacheLayout L,
                    const int* __restrict__ meta, int group, const int* __restrict__ cu_tokens,
                    const int* __restrict__ positions, bf16* __restrict__ out, float* __restrict__ part_o,
-                   float* __restrict__ part_ml, int nq, int window, float scale_log2, int num_pages, int splits,
-                   int bt_cap, int* __restrict__ status) {
+                   float* __restrict__ part_ml, int* __restrict__ counters, const float* __restrict__ inv_freq, int rot,
+                   int store_kv, int nq, int window, float scale_log2, int num_pages, int splits,
+                   int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* qtile = reinterpret_cast<bf16*>(smem_raw);
     bf16* tiles = qtile + 16 * LDS;
-    int* bt_s = reinterpret_cast<int*>(smem_raw + DEC_SMEM);
+    __shared__ int s_last;
+    pdl_launch_dependents();
     const int split = blockIdx.x, kvh = blockIdx.y, e = blockIdx.z;
-    if (e >= meta[META_NUM_ENTRIES]) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool live = e < meta[META_NUM_ENTRIES];
     const int G = nq / L.num_kv_heads;
-    const int row0 = cu_tokens[e];
-    const int kv_len = positions[row0] + 1;
+    const int row0 = live ? cu_tokens[e] : 0;
+    const int kv_len = live ? positions[row0] + 1 : 0;
     const int kstart = window > 0 ? max(0, kv_len - window) : 0;
     const int per = (((kv_len - kstart + splits - 1) / splits + DEC_KT - 1) / DEC_KT) * DEC_KT;
     const int lo = kstart + split * per, hi = min(kv_len, lo + per);
     const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)e * meta[META_BT_STRIDE + group];
-    const int page_lo = lo / L.page_size;
-    int page_cnt = lo < hi ? (hi - 1) / L.page_size - page_lo + 1 : 0;
-    if (page_cnt > bt_cap) {  // the host sized the slice for a shorter context than this request has
-        if (tid == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + hi);
-        page_cnt = bt_cap;
-    }
-    stage_block_table(bt_s, bt, page_lo, page_cnt, num_pages, tid, DEC_WARPS * 32, status);
-    const int hi_s = min(hi, (page_lo + page_cnt) * L.page_size);  // never beyond the staged slice
+    // A lane copies the same rows of every tile; the pages of a tile's rows are fetched from the block
+    // table into registers one tile ahead, so no copy waits for a table lookup.
+    constexpr int PAIRS = D / 16, RPL = DEC_KT * PAIRS / 32;  // 32-byte sectors per row; rows*sectors per lane
+    const int ps = L.page_size;
+    const int ps_shift = (ps & (ps - 1)) == 0 ? 31 - __clz(ps) : -1;
+    const size_t v_off = (size_t)L.num_kv_heads * ps * D, page_stride = 2 * v_off, head_off = (size_t)kvh * ps * D;
+    bf16* mine = tiles + warp * DEC_WARP_ELEMS;
+    const int ntiles = lo < hi ? (hi - lo + DEC_KT - 1) / DEC_KT : 0;
+    auto fetch_pages = [&](int t, int (&pg)[RPL]) {
+#pragma unroll
+        for (int i = 0; i < RPL; ++i) {
+            int pos = lo + t * DEC_KT + (lane + 32 * i) / PAIRS;
+            pg[i] = -1;
+            if (pos < hi) pg[i] = __ldg(bt + (ps_shift >= 0 ? pos >> ps_shift : pos / ps));
+        }
+    };
+    auto load_tile = [&](int t, int stage, const int (&pg)[RPL]) {
+        bf16* ktile = mine + stage * 2 * DEC_KT * LDS;
+        bf16* vtile = ktile + DEC_KT * LDS;
+#pragma unroll
+        for (int i = 0; i < RPL; ++i) {
+            int idx = lane + 32 * i, r = idx / PAIRS, c = (idx % PAIRS) * 16;
+            int pos = lo + t * DEC_KT + r;
+            int o0 = toff(r, c), o1 = toff(r, c + 8);
+            int page = pg[i];
+            if (pos < hi && (page <= 0 || page >= num_pages)) {
+                atomicExch(&status[STATUS_BAD_PAGE], 1 + pos);
+                page = -1;
+            }
+            if (page > 0) {
+                int slot = ps_shift >= 0 ? pos & (ps - 1) : pos % ps;
+                const bf16* src = cache + (size_t)page * page_stride + head_off + (size_t)slot * D + c;
+                cp_async_16(ktile + o0, src);
+                cp_async_16(ktile + o1, src + 8);
+                cp_async_16(vtile + o0, src + v_off);
+                cp_async_16(vtile + o1, src + v_off + 8);
+            } else {  // beyond the split: zeros (a value row nobody wrote must not reach P*V)
+                uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(ktile + o0) = z;
+                *reinterpret_cast<uint4*>(ktile + o1) = z;
+                *reinterpret_cast<uint4*>(vtile + o0) = z;
+                *reinterpret_cast<uint4*>(vtile + o1) = z;
+            }
+        }
+    };
+    int pg_cur[RPL], pg_nxt[RPL];
+    if (live && warp < ntiles) fetch_pages(warp, pg_cur);
+    if (live && warp + DEC_WARPS < ntiles) fetch_pages(warp + DEC_WARPS, pg_nxt);
+    // The newest position (kv_len - 1) is written during this step, by the kernel before this one
+    // or by this block; every other key is older than the step and may be fetched at once.
+    const bool first_is_old = live && warp < ntiles && lo + (warp + 1) * DEC_KT <= kv_len - 1;
+    if (first_is_old) load_tile(warp, 0, pg_cur);
+    cp_async_commit();
 
-    for (int idx = tid; idx < 16 * (D / 8); idx += DEC_WARPS * 32) {
-        int r = idx / (D / 8), c = idx % (D / 8);
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r < G) v = *reinterpret_cast<const uint4*>(q + (size_t)row0 * q_stride + (size_t)(kvh * G + r) * D + c * 8);
-        *reinterpret_cast<uint4*>(qtile + r * LDS + c * 8) = v;
+    pdl_wait();
+    if (!live) return;
+    const bool owns_newest = lo < hi && hi == kv_len;
+    if (inv_freq) {
+        const int half = rot / 2, pos = kv_len - 1;
+        const bf16* row = q + (size_t)row0 * q_stride;
+        // queries of the group, rotated into the tile (rows beyond the group are zero)
+        for (int idx = tid; idx < 16 * (D / 2); idx += DEC_WARPS * 32) {
+            int r = idx / (D / 2), i = idx % (D / 2);
+            float a = 0.f, b = 0.f;
+            if (r < G) {
+                const bf16* x = row + (size_t)(kvh * G + r) * D;
+                if (i < half) {
+                    float sn, cs;
+                    sincosf((float)pos * inv_freq[i], &sn, &cs);
+                    float xa = __bfloat162float(x[i]), xb = __bfloat162float(x[i + half]);
+                    a = xa * cs - xb * sn;
+                    b = xa * sn + xb * cs;
+                    qtile[toff(r, i)] = __float2bfloat16_rn(a);
+                    qtile[toff(r, i + half)] = __float2bfloat16_rn(b);
+                } else {
+                    // dims beyond the rotated part, two to a slot: rot + 2j and rot + 2j + 1, j = i - half
+                    int j = rot + 2 * (i - half);
+                    qtile[toff(r, j)] = x[j];
+                    qtile[toff(r, j + 1)] = x[j + 1];
+                }
+            } else {
+                qtile[toff(r, 2 * i)] = __float2bfloat16_rn(0.f);
+                qtile[toff(r, 2 * i + 1)] = __float2bfloat16_rn(0.f);
+            }
+        }
+        if (store_kv && owns_newest) {  // the newest key and value go to their page before their tile is read
+            int page = bt[pos / L.page_size];
+            if (page > 0 && page < num_pages) {
+                const int nkv = L.num_kv_heads;
+                const bf16* kx = row + (size_t)(nq + kvh) * D;
+                const bf16* vx = row + (size_t)(nq + nkv + kvh) * D;
+                bf16* kd = cache + L.offset(page, 0, kvh, pos % L.page_size);
+                bf16* vd = cache + L.offset(page, 1, kvh, pos % L.page_size);
+                for (int i = tid; i < half; i += DEC_WARPS * 32) {
+                    float sn, cs;
+                    sincosf((float)pos * inv_freq[i], &sn, &cs);
+                    float xa = __bfloat162float(kx[i]), xb = __bfloat162float(kx[i + half]);
+                    kd[i] = __float2bfloat16_rn(xa * cs - xb * sn);
+                    kd[i + half] = __float2bfloat16_rn(xa * sn + xb * cs);
+                }
+                for (int i = rot + tid; i < D; i += DEC_WARPS * 32) kd[i] = kx[i];
+                for (int i = tid; i < D; i += DEC_WARPS * 32) vd[i] = vx[i];
+                __threadfence();
+            }
+        }
+    } else {
+        for (int idx = tid; idx < 16 * (D / 8); idx += DEC_WARPS * 32) {
+            int r = idx / (D / 8), c = idx % (D / 8);
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < G) v = *reinterpret_cast<const uint4*>(q + (size_t)row0 * q_stride + (size_t)(kvh * G + r) * D + c * 8);
+            *reinterpret_cast<uint4*>(qtile + toff(r, c * 8)) = v;
+        }
     }
     __syncthreads();
+    if (warp < ntiles && !first_is_old) load_tile(warp, 0, pg_cur);
+    cp_async_commit();
+
     uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
     if (Q_IN_REGS) {
 #pragma unroll
@@ -261,20 +386,13 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
 #pragma unroll
     for (int dt = 0; dt < DTILES; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
 
-    bf16* mine = tiles + warp * DEC_WARP_ELEMS;
-    const int ntiles = lo < hi ? (hi - lo + DEC_KT - 1) / DEC_KT : 0;
-    auto load_tile = [&](int t, int stage) {
-        bf16* k = mine + stage * 2 * DEC_KT * LDS;
-        load_kv_tile(k, k + DEC_KT * LDS, cache, L, bt_s, page_lo, kvh, lo + t * DEC_KT, DEC_KT, lo, hi_s, lane, 32);
-    };
-    if (warp < ntiles) load_tile(warp, 0);
-    cp_async_commit();
     for (int t = warp, it = 0; t < ntiles; t += DEC_WARPS, ++it) {
         int stage = 0;
         if (DEC_STAGES == 2) {
             stage = it & 1;
-            if (t + DEC_WARPS < ntiles) load_tile(t + DEC_WARPS, stage ^ 1);
+            if (t + DEC_WARPS < ntiles) load_tile(t + DEC_WARPS, stage ^ 1, pg_nxt);
             cp_async_commit();
+            if (t + 2 * DEC_WARPS < ntiles) fetch_pages(t + 2 * DEC_WARPS, pg_nxt);  // arrives while this tile is computed
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
@@ -296,7 +414,10 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
         pv_tile<DEC_NK>(o, s, vtile, lane);
         __syncwarp();
         if (DEC_STAGES == 1) {
-            if (t + DEC_WARPS < ntiles) load_tile(t + DEC_WARPS, 0);
+            if (t + DEC_WARPS < ntiles) {
+                load_tile(t + DEC_WARPS, 0, pg_nxt);
+                if (t + 2 * DEC_WARPS < ntiles) fetch_pages(t + 2 * DEC_WARPS, pg_nxt);
+            }
             cp_async_commit();
         }
     }
@@ -340,26 +461,50 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
             if (i == 0) { part_ml[slot * 2] = mx; part_ml[slot * 2 + 1] = lsum; }
         }
     }
-}
-
-// Merges the splits of attn_decode: out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).
-__global__ void attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                    const int* __restrict__ meta, const int* __restrict__ cu_tokens,
-                                    bf16* __restrict__ out, int nq, int splits) {
-    const int head = blockIdx.x, e = blockIdx.y;
-    if (e >= meta[META_NUM_ENTRIES]) return;
-    const size_t base = ((size_t)e * nq + head) * splits;
-    float mx = -INFINITY;
-    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, part_ml[(base + s) * 2]);
-    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    if (splits == 1) return;
+    // count this block in; the last one merges the splits of its (request, head group)
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int* c = counters + e * L.num_kv_heads + kvh;
+        int old = atomicAdd(c, 1);
+        s_last = old == splits - 1;
+        if (s_last) *c = 0;  // as it was found, for the next launch
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // All loads of the merge are independent: first the (max, sum) pairs of every (head, split) into
+    // shared memory, then every thread walks the splits of its (head, dim) eight loads at a time.
+    float* ml = reinterpret_cast<float*>(tiles);  // [G][splits][2]
+    for (int idx = tid; idx < G * splits * 2; idx += DEC_WARPS * 32) {
+        int r = idx / (splits * 2), j = idx % (splits * 2);
+        ml[idx] = __ldcg(part_ml + (((size_t)e * nq + kvh * G + r) * splits) * 2 + j);
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * D; idx += DEC_WARPS * 32) {
+        int r = idx / D, i = idx % D;
+        const int head = kvh * G + r;
+        const float* po = part_o + (((size_t)e * nq + head) * splits) * D + i;
+        const float* mlr = ml + r * splits * 2;
+        float mx = -INFINITY;
+        for (int s = 0; s < splits; ++s) mx = fmaxf(mx, mlr[2 * s]);
         float lsum = 0.f, acc = 0.f;
-        if (mx > -INFINITY)
-            for (int s = 0; s < splits; ++s) {
-                float f = fast_exp2(part_ml[(base + s) * 2] - mx);
-                lsum += part_ml[(base + s) * 2 + 1] * f;
-                acc += part_o[(base + s) * D + i] * f;
+        if (mx > -INFINITY) {
+            for (int s0 = 0; s0 < splits; s0 += 8) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] = s0 + j < splits ? __ldcg(po + (size_t)(s0 + j) * D) : 0.f;
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (s0 + j < splits) {
+                        float f = fast_exp2(mlr[2 * (s0 + j)] - mx);
+                        lsum += mlr[2 * (s0 + j) + 1] * f;
+                        acc += v[j] * f;
+                    }
             }
-        out[((size_t)cu_tokens[e] * nq + head) * D + i] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+        }
+        out[((size_t)row0 * nq + head) * D + i] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
     }
 }
 
@@ -381,6 +526,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     bf16* qtile = reinterpret_cast<bf16*>(smem_raw);
     bf16* kv = qtile + PF_ROWS * LDS;
     int* bt_s = reinterpret_cast<int*>(smem_raw + PF_SMEM);
+    pdl_launch_dependents();
+    pdl_wait();
     const int qt = blockIdx.x, kvh = blockIdx.y, e = blockIdx.z;
     if (e >= meta[META_NUM_ENTRIES]) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -398,7 +545,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (tok < nt)
             v = *reinterpret_cast<const uint4*>(q + (size_t)(row0 + t0 + tok) * q_stride + (size_t)(kvh * G + hd) * D + c * 8);
-        *reinterpret_cast<uint4*>(qtile + r * LDS + c * 8) = v;
+        *reinterpret_cast<uint4*>(qtile + toff(r, c * 8)) = v;
     }
     const int p_first = ctx + t0, p_last = p_first + nt - 1;
     const int kbeg = window > 0 ? max(0, p_first - window + 1) : 0, kend = p_last + 1;
@@ -488,6 +635,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
 
 // ----------------------------------------------------------------------------- host side
 extern "C" int attn_head_dim() { return D; }
+// How many decode blocks fit a multiprocessor (by shared memory): the host sizes the splits by it.
+extern "C" int attn_decode_blocks_per_sm() { return DEC_BLOCKS_PER_SM; }
 
 // Float32 words of scratch that attn_decode needs for `splits` > 1: partial outputs and (max, sum) pairs.
 extern "C" size_t attn_decode_scratch_floats(int S, int nq, int splits) {
@@ -514,39 +663,35 @@ extern "C" int attn_prefill(const void* q, int q_stride, const void* cache, cons
         if (err != cudaSuccess) return (int)err;
         configured = smem;
     }
-    attn_prefill_kernel<<<grid, 128, smem, stream>>>((const bf16*)q, q_stride, (const bf16*)cache, L, meta, group, cu_tokens,
-                                                      ctx_lens, (bf16*)out, nq, window, scale * LOG2E, num_pages, bt_cap, status);
-    LAUNCH_RETURN();
+    return (int)launch_kernel(attn_prefill_kernel, grid, 128, smem, stream, (const bf16*)q, q_stride, (const bf16*)cache, L, meta,
+                              group, cu_tokens, ctx_lens, (bf16*)out, nq, window, scale * LOG2E, num_pages, bt_cap, status);
 }
 
+// `scratch`: attn_decode_scratch_floats(...) floats when splits > 1.  `counters`: S * nkv ints, zero before the
+// first launch (the kernel leaves them zero).  `inv_freq` (rot/2 floats) switches the fused rotation on: q is
+// then the unrotated projection row and, with store_kv, the new key and value are written here too.
 extern "C" int attn_decode(const void* q, int q_stride, const void* cache, const int* meta, int group,
-                           const int* cu_tokens, const int* positions, void* out, float* scratch, int S, int nq, int nkv,
-                           int page_size, int num_pages, int window, float scale, int splits, int max_context,
-                           int* status, cudaStream_t stream) {
+                           const int* cu_tokens, const int* positions, void* out, float* scratch, int* counters,
+                           const float* inv_freq, int rot, int store_kv, int S, int nq, int nkv, int page_size,
+                           int num_pages, int window, float scale, int splits, int max_context, int* status,
+                           cudaStream_t stream) {
     if (S <= 0) return 0;
     if (nq % nkv || nq / nkv > 16 || splits < 1) return (int)cudaErrorInvalidValue;
-    if (splits > 1 && !scratch) return (int)cudaErrorInvalidValue;
+    if (splits > 1 && (!scratch || !counters)) return (int)cudaErrorInvalidValue;
+    if (inv_freq && (rot % 2 || rot > D || rot <= 0)) return (int)cudaErrorInvalidValue;
     CacheLayout L{nkv, page_size, D};
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)S * nq * splits * D : nullptr;
-    int span = window > 0 ? min(max_context, window) : max_context;
-    int per = (((span + splits - 1) / splits + DEC_KT - 1) / DEC_KT) * DEC_KT;  // keys of one split at most
-    int bt_cap = per / page_size + 2;
-    size_t smem = DEC_SMEM + (size_t)bt_cap * sizeof(int);
-    if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
-    static size_t configured = 0;
-    if (smem > configured) {
+    (void)max_context;
+    const size_t smem = DEC_SMEM;
+    static bool configured = false;  // once: the attribute is not set again inside a stream capture
+    if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
-        configured = smem;
+        configured = true;
     }
     dim3 grid(splits, nkv, S);
-    attn_decode_kernel<<<grid, DEC_WARPS * 32, smem, stream>>>((const bf16*)q, q_stride, (const bf16*)cache, L, meta, group,
-                                                               cu_tokens, positions, (bf16*)out, part_o, part_ml, nq,
-                                                               window, scale * LOG2E, num_pages, splits, bt_cap, status);
-    if (splits > 1) {
-        dim3 cgrid(nq, S);
-        attn_combine_kernel<<<cgrid, D < 128 ? D : 128, 0, stream>>>(part_o, part_ml, meta, cu_tokens, (bf16*)out, nq, splits);
-    }
-    LAUNCH_RETURN();
+    return (int)launch_kernel(attn_decode_kernel, grid, DEC_WARPS * 32, smem, stream, (bf16*)q, q_stride, (bf16*)cache, L, meta,
+                              group, cu_tokens, positions, (bf16*)out, part_o, part_ml, counters, inv_freq, rot, store_kv, nq,
+                              window, scale * LOG2E, num_pages, splits, status);
 }

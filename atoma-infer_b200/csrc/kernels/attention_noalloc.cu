@@ -11,10 +11,14 @@
 // symbol calls, not an address a kernel could use: the device address comes from
 // cudaGetSymbolAddress below, once per device.
 static __device__ __align__(256) float g_noalloc_scratch[ATTN_NOALLOC_SCRATCH_FLOATS];
+// Arrival counters of the splits, one per (request, key/value head).  They must be zero when a
+// launch starts: the loader zero-fills the array and every launch leaves it zero again.
+static __device__ __align__(256) int g_noalloc_counters[ATTN_NOALLOC_MAX_GROUPS];
 
 namespace {
 constexpr int kMaxDevices = 64;
 float* g_scratch_ptr[kMaxDevices] = {};  // device address of the array, per device ordinal
+int* g_counters_ptr[kMaxDevices] = {};
 
 int fail(int code, char* err, int cap, const char* msg) {
     if (err && cap > 0) snprintf(err, (size_t)cap, "%s", msg);
@@ -30,6 +34,11 @@ extern "C" int attn_decode_noalloc(const void* q, int q_stride, const void* cach
     if (S <= 0 || nq <= 0 || nkv <= 0 || splits < 1 || page_size <= 0)
         return fail(ATTN_NOALLOC_BAD_ARGUMENT, err, err_cap, "attn_decode_noalloc: S, heads, splits and page_size must be positive");
     const size_t need = attn_decode_scratch_floats(S, nq, splits);
+    if ((size_t)S * nkv > (size_t)ATTN_NOALLOC_MAX_GROUPS) {
+        snprintf(msg, sizeof msg, "attn_decode_noalloc: %d requests x %d key/value heads exceed the %d built-in split counters",
+                 S, nkv, ATTN_NOALLOC_MAX_GROUPS);
+        return fail(ATTN_NOALLOC_TOO_LARGE, err, err_cap, msg);
+    }
     if (need > (size_t)ATTN_NOALLOC_SCRATCH_FLOATS) {
         snprintf(msg, sizeof msg,
                  "attn_decode_noalloc: %d requests x %d heads x %d splits x (%d + 2) = %zu floats of scratch, the built-in "
@@ -51,10 +60,19 @@ extern "C" int attn_decode_noalloc(const void* q, int q_stride, const void* cach
                      cudaGetErrorString(e));
             return fail(e != cudaSuccess ? (int)e : ATTN_NOALLOC_BAD_ARGUMENT, err, err_cap, msg);
         }
+        int* c = nullptr;
+        e = cudaGetSymbolAddress((void**)&c, g_noalloc_counters);
+        if (e != cudaSuccess || !c) {
+            snprintf(msg, sizeof msg, "attn_decode_noalloc: cudaGetSymbolAddress failed on device %d (%s)", dev,
+                     cudaGetErrorString(e));
+            return fail(e != cudaSuccess ? (int)e : ATTN_NOALLOC_BAD_ARGUMENT, err, err_cap, msg);
+        }
+        g_counters_ptr[dev] = c;
         g_scratch_ptr[dev] = p;
     }
-    int rc = attn_decode(q, q_stride, cache, meta, group, cu_tokens, positions, out, g_scratch_ptr[dev], S, nq, nkv,
-                         page_size, num_pages, window, scale, splits, max_context, status, stream);
+    int rc = attn_decode(q, q_stride, cache, meta, group, cu_tokens, positions, out, g_scratch_ptr[dev],
+                         g_counters_ptr[dev], nullptr, 0, 0, S, nq, nkv, page_size, num_pages, window, scale, splits,
+                         max_context, status, stream);
     if (rc != 0) {
         snprintf(msg, sizeof msg, "attn_decode_noalloc: launch failed (%s)", cudaGetErrorString((cudaError_t)rc));
         return fail(rc, err, err_cap, msg);

@@ -21,15 +21,19 @@
 //    cudaGetSymbolAddress) and sets the kernel's shared-memory attribute; make that
 //    first call outside any stream capture.  Later calls do neither.
 //  * It calls no cudaMalloc, cudaFree or any allocating routine, on any path.
-//  * All calls share the one array and it keeps what the last call left.  Nothing
-//    in it has to start at zero: every (request, head, split) slot that the merge
-//    step reads is written by the same call first, empty splits included.  Two
+//    Also S * num_kv_heads must not exceed ATTN_NOALLOC_MAX_GROUPS (4096).
+//  * All calls share the one array and it keeps what the last call left.  The
+//    partial results need no clearing: every (request, head, split) slot that the
+//    merge reads is written by the same call first, empty splits included.  The
+//    small array of arrival counters beside it must be zero when a call starts; it
+//    is zero when the library is loaded and every call leaves it zero.  Two
 //    calls whose kernels overlap on the GPU (different streams) race on it: keep
 //    calls on one stream, or order them yourself.
 #pragma once
 #include <cuda_runtime.h>
 
 #define ATTN_NOALLOC_SCRATCH_FLOATS (1u << 20)
+#define ATTN_NOALLOC_MAX_GROUPS 4096  // requests x key/value heads of one call
 #define ATTN_NOALLOC_TOO_LARGE (-1)
 #define ATTN_NOALLOC_BAD_ARGUMENT (-2)
 

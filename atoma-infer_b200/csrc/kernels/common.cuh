@@ -83,3 +83,32 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 #define LAUNCH_RETURN() return (int)cudaGetLastError()
+
+// ----------------------------------------------------------------------------- dependent launches
+// Kernels of a step run back to back on one stream.  Launched with programmatic stream
+// serialization, a kernel may start while its predecessor is still draining: what it does
+// before pdl_wait() (index arithmetic, loads of weights, which no kernel writes) overlaps the
+// predecessor's tail; pdl_wait() returns once all earlier kernels have finished and their
+// writes are visible.  Every kernel calls pdl_launch_dependents() at its start and pdl_wait()
+// before it reads anything an earlier kernel wrote or writes anything an earlier kernel
+// reads.  Without the launch attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern int g_use_pdl;  // one per library (defined in its main file), set through kernels_set_pdl
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                        cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -12,12 +12,17 @@
 // (csrc/kernels/flash_fwd_kernel.h).
 #include "common.cuh"
 
+int g_use_pdl = 1;
+extern "C" void kernels_set_pdl(int on) { g_use_pdl = on ? 1 : 0; }
+
 // ----------------------------------------------------------------------------- embedding
 // resid[t, :] = table[tokens[t], :], widened to float32 (the residual stream is float32).
 template <typename T>
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                   float* __restrict__ resid, const int* __restrict__ meta, int H, int V,
                                   int* __restrict__ status) {
+    pdl_launch_dependents();
+    pdl_wait();
     int t = blockIdx.x;
     if (t >= meta[META_NUM_TOKENS]) return;
     int tok = tokens[t];
@@ -33,27 +38,67 @@ extern "C" int embed_rows(const int* tokens, const void* table, int table_dtype,
     if (T <= 0) return 0;
     int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == DT_F32)
-        embed_rows_kernel<float><<<T, threads, 0, stream>>>(tokens, (const float*)table, resid, meta, H, V, status);
-    else
-        embed_rows_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(tokens, (const __nv_bfloat16*)table, resid, meta, H, V, status);
-    LAUNCH_RETURN();
+        return (int)launch_kernel(embed_rows_kernel<float>, T, threads, 0, stream, tokens, (const float*)table, resid, meta, H, V, status);
+    return (int)launch_kernel(embed_rows_kernel<__nv_bfloat16>, T, threads, 0, stream, tokens, (const __nv_bfloat16*)table, resid,
+                              meta, H, V, status);
 }
 
 // ----------------------------------------------------------------------------- RMSNorm
 // resid[t] += delta[t] (if delta), out[t] = resid[t] * rsqrt(mean(resid[t]^2) + eps) * w.
 // With `rows`: works on rows[r] of resid/delta, writes out[r], leaves resid untouched.
 template <typename TD, typename TO>
-__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta,
-                                   const int* __restrict__ rows, const float* __restrict__ w, float eps,
-                                   TO* __restrict__ out, const int* __restrict__ meta, int H) {
+__global__ void __launch_bounds__(256)
+add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const int* __restrict__ rows,
+                   const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ meta, int H) {
     __shared__ float red[33];
+    pdl_launch_dependents();
+    constexpr int MAXV = 4;  // up to 4 x 4 values per thread stay in registers (H <= 16 * blockDim)
+    const bool in_regs = (H % 4 == 0) && H <= 4 * MAXV * (int)blockDim.x;
+    float4 wv[MAXV];
+    if (in_regs) {  // the norm weight depends on no earlier kernel: fetched before the wait
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+            int i = (threadIdx.x + j * blockDim.x) * 4;
+            if (i < H) wv[j] = *reinterpret_cast<const float4*>(w + i);
+        }
+    }
+    pdl_wait();
     int r = blockIdx.x;
     int limit = rows ? meta[META_NUM_ROWS] : meta[META_NUM_TOKENS];
     if (r >= limit) return;
     size_t src = rows ? (size_t)rows[r] : (size_t)r;
     float* x = resid + src * H;
     const TD* dl = delta ? delta + src * H : nullptr;
+    TO* o = out + (size_t)r * H;
     float ss = 0.f;
+    if (in_regs) {
+        float4 v[MAXV];
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+            int i = (threadIdx.x + j * blockDim.x) * 4;
+            if (i < H) {
+                v[j] = *reinterpret_cast<const float4*>(x + i);
+                if (dl) {
+                    v[j].x += to_float(dl[i]); v[j].y += to_float(dl[i + 1]);
+                    v[j].z += to_float(dl[i + 2]); v[j].w += to_float(dl[i + 3]);
+                    if (!rows) *reinterpret_cast<float4*>(x + i) = v[j];
+                }
+                ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+                ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+            }
+        }
+        ss = block_sum(ss, red);
+        float inv = rsqrtf(ss / (float)H + eps);
+#pragma unroll
+        for (int j = 0; j < MAXV; ++j) {
+            int i = (threadIdx.x + j * blockDim.x) * 4;
+            if (i < H) {
+                o[i] = from_float<TO>(v[j].x * inv * wv[j].x); o[i + 1] = from_float<TO>(v[j].y * inv * wv[j].y);
+                o[i + 2] = from_float<TO>(v[j].z * inv * wv[j].z); o[i + 3] = from_float<TO>(v[j].w * inv * wv[j].w);
+            }
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = x[i];
         if (dl) {
@@ -64,7 +109,6 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restri
     }
     ss = block_sum(ss, red);
     float inv = rsqrtf(ss / (float)H + eps);
-    TO* o = out + (size_t)r * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = x[i];
         if (dl && rows) v += to_float(dl[i]);
@@ -78,13 +122,13 @@ extern "C" int add_rmsnorm(float* resid, const void* delta, int delta_dtype, con
     if (n <= 0) return 0;
     int threads = H >= 1024 ? 256 : 128;
 #define NORM_CASE(TD, TO) \
-    add_rmsnorm_kernel<TD, TO><<<n, threads, 0, stream>>>(resid, (const TD*)delta, rows, w, eps, (TO*)out, meta, H)
+    return (int)launch_kernel(add_rmsnorm_kernel<TD, TO>, n, threads, 0, stream, resid, (const TD*)delta, rows, w, eps, \
+                              (TO*)out, meta, H)
     if (delta_dtype == DT_F32 && out_dtype == DT_F32) NORM_CASE(float, float);
     else if (delta_dtype == DT_BF16 && out_dtype == DT_BF16) NORM_CASE(__nv_bfloat16, __nv_bfloat16);
     else if (delta_dtype == DT_F32 && out_dtype == DT_BF16) NORM_CASE(float, __nv_bfloat16);
     else NORM_CASE(__nv_bfloat16, float);
 #undef NORM_CASE
-    LAUNCH_RETURN();
 }
 
 // ----------------------------------------------------------------------------- float32 GEMM
@@ -97,6 +141,8 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__
                                                        float* __restrict__ y, int M, int N, int K) {
     __shared__ float xs[GK][GB + 4];
     __shared__ float ws[GK][GB + 4];
+    pdl_launch_dependents();
+    pdl_wait();
     int m0 = blockIdx.y * GB, n0 = blockIdx.x * GB;
     int tx = threadIdx.x % 16, ty = threadIdx.x / 16;  // 16 x 16 threads, 4 x 4 outputs each
     float acc[4][4] = {};
@@ -139,8 +185,7 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__
 extern "C" int gemm_f32(const float* x, const float* w, float* y, int M, int N, int K, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     dim3 grid((N + GB - 1) / GB, (M + GB - 1) / GB);
-    gemm_f32_kernel<<<grid, 256, 0, stream>>>(x, w, y, M, N, K);
-    LAUNCH_RETURN();
+    return (int)launch_kernel(gemm_f32_kernel, grid, 256, 0, stream, x, w, y, M, N, K);
 }
 
 // ----------------------------------------------------------------------------- rotation + cache write
@@ -154,50 +199,41 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int* __restrict_
                                      const int* __restrict__ token_entry, const int* __restrict__ meta, int group,
                                      const float* __restrict__ inv_freq, T* __restrict__ cache, CacheLayout L,
                                      int nq, int rot, int store_kv, int num_pages, int* __restrict__ status) {
-    int t = blockIdx.x;
-    if (t >= meta[META_NUM_TOKENS]) return;
+    // one block per (token, head of the fused row): q heads, then k heads, then v heads
+    pdl_launch_dependents();
     const int d = L.head_dim, nkv = L.num_kv_heads, half = rot / 2;
+    const int t = blockIdx.x, h = blockIdx.y;
+    const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
+    float freq = 0.f;
+    if (!(!is_q && !is_k) && (int)threadIdx.x < half) freq = inv_freq[threadIdx.x];  // a constant: before the wait
+    pdl_wait();
+    if (t >= meta[META_NUM_TOKENS]) return;
+    if (!is_q && !store_kv) return;
     const int pos = positions[t];
-    T* row = qkv + (size_t)t * (nq + 2 * nkv) * d;
-    int page = 0, slot = 0;
-    if (store_kv) {
+    T* x = qkv + ((size_t)t * (nq + 2 * nkv) + h) * d;
+    T* dst = x;  // q is rotated in place
+    if (!is_q) {
         const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)token_entry[t] * meta[META_BT_STRIDE + group];
-        page = bt[pos / L.page_size];
-        slot = pos % L.page_size;
+        int page = bt[pos / L.page_size];
         if (page <= 0 || page >= num_pages) {
             if (threadIdx.x == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + t);
-            store_kv = 0;
+            return;
         }
+        dst = cache + L.offset(page, is_k ? 0 : 1, is_k ? h - nq : h - nq - nkv, pos % L.page_size);
     }
-    // rotated pairs of q and k heads
-    int pairs = (nq + nkv) * half;
-    for (int idx = threadIdx.x; idx < pairs; idx += blockDim.x) {
-        int h = idx / half, i = idx % half;
-        float ang = (float)pos * inv_freq[i];
-        float s, c;
-        sincosf(ang, &s, &c);
-        T* x = row + (size_t)h * d;
-        float a = to_float(x[i]), b = to_float(x[i + half]);
-        T ra = from_float<T>(a * c - b * s), rb = from_float<T>(a * s + b * c);
-        if (h < nq) {
-            x[i] = ra;
-            x[i + half] = rb;
-        } else if (store_kv) {
-            T* dst = cache + L.offset(page, 0, h - nq, slot);
-            dst[i] = ra;
-            dst[i + half] = rb;
+    if (is_q || is_k) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            float f = i == (int)threadIdx.x ? freq : inv_freq[i];
+            float sn, cs;
+            sincosf((float)pos * f, &sn, &cs);
+            float a = to_float(x[i]), b = to_float(x[i + half]);
+            dst[i] = from_float<T>(a * cs - b * sn);
+            dst[i + half] = from_float<T>(a * sn + b * cs);
         }
-    }
-    if (!store_kv) return;
-    // dims of k beyond the rotated part, and all of v
-    int tail = d - rot;
-    for (int idx = threadIdx.x; idx < nkv * tail; idx += blockDim.x) {
-        int h = idx / tail, i = rot + idx % tail;
-        cache[L.offset(page, 0, h, slot) + i] = row[(size_t)(nq + h) * d + i];
-    }
-    for (int idx = threadIdx.x; idx < nkv * d; idx += blockDim.x) {
-        int h = idx / d, i = idx % d;
-        cache[L.offset(page, 1, h, slot) + i] = row[(size_t)(nq + nkv + h) * d + i];
+        if (is_k)
+            for (int i = rot + threadIdx.x; i < d; i += blockDim.x) dst[i] = x[i];  // dims beyond the rotated part
+    } else {
+        for (int i = threadIdx.x; i < d; i += blockDim.x) dst[i] = x[i];
     }
 }
 
@@ -206,15 +242,14 @@ extern "C" int rope_kv_store(void* qkv, int dtype, const int* positions, const i
                              int d, int rot, int page_size, int store_kv, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
     CacheLayout L{nkv, page_size, d};
-    int threads = 128;
+    int threads = d >= 128 ? 64 : 32;
+    dim3 grid(T, nq + 2 * nkv);
     if (dtype == DT_F32)
-        rope_kv_store_kernel<float><<<T, threads, 0, stream>>>((float*)qkv, positions, token_entry, meta, group, inv_freq,
-                                                                (float*)cache, L, nq, rot, store_kv, num_pages, status);
-    else
-        rope_kv_store_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((__nv_bfloat16*)qkv, positions, token_entry, meta,
-                                                                        group, inv_freq, (__nv_bfloat16*)cache, L, nq,
-                                                                        rot, store_kv, num_pages, status);
-    LAUNCH_RETURN();
+        return (int)launch_kernel(rope_kv_store_kernel<float>, grid, threads, 0, stream, (float*)qkv, positions, token_entry,
+                                  meta, group, inv_freq, (float*)cache, L, nq, rot, store_kv, num_pages, status);
+    return (int)launch_kernel(rope_kv_store_kernel<__nv_bfloat16>, grid, threads, 0, stream, (__nv_bfloat16*)qkv, positions,
+                              token_entry, meta, group, inv_freq, (__nv_bfloat16*)cache, L, nq, rot, store_kv, num_pages,
+                              status);
 }
 
 // ----------------------------------------------------------------------------- attention over the cache
@@ -232,6 +267,8 @@ attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__
                     const int* __restrict__ meta, int group, const int* __restrict__ token_entry,
                     const int* __restrict__ positions, T* __restrict__ out, int nq, int window, float scale,
                     int num_pages, int* __restrict__ status) {
+    pdl_launch_dependents();
+    pdl_wait();
     int t = blockIdx.x, h = blockIdx.y;
     if (t >= meta[META_NUM_TOKENS]) return;
     const int d = L.head_dim, ps = L.page_size, tid = threadIdx.x;
@@ -320,26 +357,27 @@ extern "C" int attn_generic(const void* q, int q_stride, const void* cache, int 
             if (e != cudaSuccess) return (int)e;
             configured_f32 = smem;
         }
-        attn_generic_kernel<float><<<grid, ATTN_THREADS, smem, stream>>>(
-            (const float*)q, q_stride, (const float*)cache, L, meta, group, token_entry, positions, (float*)out, nq,
-            window, scale, num_pages, status);
+        return (int)launch_kernel(attn_generic_kernel<float>, grid, ATTN_THREADS, smem, stream, (const float*)q, q_stride,
+                                  (const float*)cache, L, meta, group, token_entry, positions, (float*)out, nq, window, scale,
+                                  num_pages, status);
     } else {
         if (smem > configured_bf16) {
             e = cudaFuncSetAttribute(attn_generic_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return (int)e;
             configured_bf16 = smem;
         }
-        attn_generic_kernel<__nv_bfloat16><<<grid, ATTN_THREADS, smem, stream>>>(
-            (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, L, meta, group, token_entry, positions,
-            (__nv_bfloat16*)out, nq, window, scale, num_pages, status);
+        return (int)launch_kernel(attn_generic_kernel<__nv_bfloat16>, grid, ATTN_THREADS, smem, stream,
+                                  (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, L, meta, group, token_entry,
+                                  positions, (__nv_bfloat16*)out, nq, window, scale, num_pages, status);
     }
-    LAUNCH_RETURN();
 }
 
 // ----------------------------------------------------------------------------- SwiGLU gate
 // out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(z) = z / (1 + exp(-z))  (models/src/llama.rs:364).
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, const int* __restrict__ meta, int I) {
+    pdl_launch_dependents();
+    pdl_wait();
     int t = blockIdx.y;
     if (t >= meta[META_NUM_TOKENS]) return;
     int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -351,9 +389,9 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, c
 extern "C" int silu_mul(const void* gu, void* out, int dtype, const int* meta, int T, int I, cudaStream_t stream) {
     if (T <= 0) return 0;
     dim3 grid((I + 255) / 256, T);
-    if (dtype == DT_F32) silu_mul_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, meta, I);
-    else silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, meta, I);
-    LAUNCH_RETURN();
+    if (dtype == DT_F32) return (int)launch_kernel(silu_mul_kernel<float>, grid, 256, 0, stream, (const float*)gu, (float*)out, meta, I);
+    return (int)launch_kernel(silu_mul_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
+                              meta, I);
 }
 
 // ----------------------------------------------------------------------------- casts

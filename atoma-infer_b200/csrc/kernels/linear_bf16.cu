@@ -74,14 +74,26 @@ linear_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
     const int nblocks_all = (K + 31) / 32;
     const int per_split = (nblocks_all + ksplits - 1) / ksplits;
     const int kb_begin = blockIdx.y * per_split, nblocks = min(nblocks_all, kb_begin + per_split);
-    for (int kb0 = kb_begin + warp * SM_UNROLL; kb0 < nblocks; kb0 += SM_WARPS * SM_UNROLL) {
-        uint4 va[SM_UNROLL], vb[SM_UNROLL], vx[SM_UNROLL][NT];
+    uint4 va[SM_UNROLL], vb[SM_UNROLL];
+    auto load_weights = [&](int kb0) {
 #pragma unroll
         for (int u = 0; u < SM_UNROLL; ++u) {
             int k = (kb0 + u) * 32 + tig * 8;
             bool ok = kb0 + u < nblocks && k < K;  // K is a multiple of 8: a 16-byte chunk is all inside or all outside
             va[u] = ok ? ldg_stream(wa + k) : make_uint4(0u, 0u, 0u, 0u);
             vb[u] = ok ? ldg_stream(wb + k) : make_uint4(0u, 0u, 0u, 0u);
+        }
+    };
+    int kb0 = kb_begin + warp * SM_UNROLL;
+    pdl_launch_dependents();
+    if (kb0 < nblocks) load_weights(kb0);  // weights depend on no earlier kernel: in flight before the wait
+    pdl_wait();                            // x is what the kernel before wrote
+    while (kb0 < nblocks) {
+        uint4 vx[SM_UNROLL][NT];
+#pragma unroll
+        for (int u = 0; u < SM_UNROLL; ++u) {
+            int k = (kb0 + u) * 32 + tig * 8;
+            bool ok = kb0 + u < nblocks && k < K;
 #pragma unroll
             for (int t = 0; t < NT; ++t)
                 vx[u][t] = (ok && xok[t]) ? *reinterpret_cast<const uint4*>(xr[t] + k) : make_uint4(0u, 0u, 0u, 0u);
@@ -93,6 +105,8 @@ linear_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
                 mma16816(acc[t], va[u].x, vb[u].x, va[u].y, vb[u].y, vx[u][t].x, vx[u][t].y);
                 mma16816(acc[t], va[u].z, vb[u].z, va[u].w, vb[u].w, vx[u][t].z, vx[u][t].w);
             }
+        kb0 += SM_WARPS * SM_UNROLL;
+        if (kb0 < nblocks) load_weights(kb0);
     }
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
@@ -165,13 +179,16 @@ extern "C" int linear_skinny(const void* x, const void* w, void* y, int out_dtyp
     cfg.gridDim = dim3(tiles, ksplits, 1);
     cfg.blockDim = dim3(SM_WARPS * 32, 1, 1);
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = ksplits;
     attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = ksplits > 1 ? 1 : 0;  // a plain launch when no cluster is needed
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    // a cluster only when K is split; the dependent-launch attribute when it is switched on
+    cfg.attrs = ksplits > 1 ? attr : attr + 1;
+    cfg.numAttrs = (ksplits > 1 ? 1 : 0) + (g_use_pdl ? 1 : 0);
     cudaError_t err;
 #define SMALL(TO, NT, EPI) err = cudaLaunchKernelEx(&cfg, linear_small_kernel<TO, NT, EPI>, xb, wb, (TO*)y, M, N, K, ksplits)
     if (epilogue == 1) {

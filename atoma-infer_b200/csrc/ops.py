@@ -9,6 +9,7 @@ its linears to cuBLAS through candle (models/src/llama.rs:269-271).
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -54,6 +55,13 @@ class CudaOps:
         self.status = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=self.device)
         self.launches = 0  # own kernel launches, counted for the benchmark record
         self._attn_libs = {}
+        self._counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # split arrivals; kernels leave zeros
+        # Programmatic dependent launch lets a kernel start while its predecessor drains.  Measured on
+        # the decode step of Llama 3.2 1B it made the step slower (1.17 ms against 0.97 ms), so it is
+        # off unless ATOMA_INFER_PDL=1; ATOMA_INFER_FUSED_ROPE=0 switches the fused rotation off.
+        self.pdl = os.environ.get("ATOMA_INFER_PDL", "0") == "1"
+        self.fused_rope = os.environ.get("ATOMA_INFER_FUSED_ROPE", "1") != "0"
+        self.lib.kernels_set_pdl(int(self.pdl))
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
 
     # ------------------------------------------------------------------ helpers
@@ -64,6 +72,12 @@ class CudaOps:
         self.launches += 1
         if err:
             raise KernelError(f"{what}: CUDA error {err}")
+
+    def set_pdl(self, on: bool) -> None:
+        self.pdl = bool(on)
+        self.lib.kernels_set_pdl(int(on))
+        for lib in self._attn_libs.values():
+            lib.kernels_set_pdl(int(on))
 
     def check_status(self) -> None:
         """Raises if a kernel of an earlier launch met a bad token id or page id (synchronises)."""
@@ -128,26 +142,37 @@ class CudaOps:
                                            _p(inv_freq), _p(cache_layer), num_pages, T, nq, nkv, d, rot, page_size,
                                            int(store_kv), _p(self.status), self._stream()), "rope_kv_store")
 
+    def fast_attention(self, dtype, d: int, nq: int, nkv: int, q_stride: int) -> bool:
+        """Whether the tensor-core attention kernels take this geometry."""
+        return (dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and nq % nkv == 0 and nq // nkv <= 16
+                and q_stride % 8 == 0)
+
     def attention(self, q, q_stride: int, cache_layer, ctx, group: int, out, nq: int, nkv: int, d: int,
-                  page_size: int, num_pages: int, window: int, scale: float):
+                  page_size: int, num_pages: int, window: int, scale: float, rope=None):
         """Attention of the step's queries over what their requests have cached (the step's own
         keys included).  bfloat16 with a head size in steps of 16 up to 256 runs the tensor-core
         kernels (one library per head size, built at first use); anything else, and all of
-        float32, runs the plain kernel."""
+        float32, runs the plain kernel.  ``rope`` = (inv_freq, rotary_dim, store_kv): only for decode
+        steps on the fast path (see ``fast_attention``); the queries are then still unrotated and the
+        kernel rotates them, and writes the new key and value, itself."""
         T, S = ctx.T, ctx.S
-        groups_ok = nq % nkv == 0 and nq // nkv <= 16
-        if q.dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and groups_ok and q_stride % 8 == 0:
+        if rope is not None and not (ctx.decode_only and self.fast_attention(q.dtype, d, nq, nkv, q_stride)):
+            raise KernelError("fused rotation exists for decode steps on the bfloat16 fast path only")
+        if self.fast_attention(q.dtype, d, nq, nkv, q_stride):
             lib = self._attention_library(d)
             if ctx.decode_only:
-                splits = self.decode_splits(S, nkv, ctx.max_context)
+                splits = self.decode_splits(S, nkv, ctx.max_context, lib.attn_decode_blocks_per_sm())
                 n = lib.attn_decode_scratch_floats(S, nq, splits)
                 scratch = torch.empty(n, dtype=torch.float32, device=q.device) if n else None
+                if S * nkv > self._counters.numel():
+                    raise KernelError(f"decode attention: {S} requests x {nkv} heads exceed the split counters")
+                inv_freq, rot, store = rope if rope is not None else (None, 0, False)
                 self._check(lib.attn_decode(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
-                                            _p(ctx.positions), _p(out), _p(scratch), S, nq, nkv, page_size, num_pages,
+                                            _p(ctx.positions), _p(out), _p(scratch), _p(self._counters), _p(inv_freq),
+                                            rot, int(store), S, nq, nkv, page_size, num_pages,
                                             window, ctypes.c_float(scale), splits, ctx.max_context, _p(self.status),
                                             self._stream()),
                             "attn_decode")
-                self.launches += int(splits > 1)
             else:
                 self._check(lib.attn_prefill(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
                                              _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
@@ -166,18 +191,31 @@ class CudaOps:
         if lib is None:
             lib = build.load_library(f"attention_d{d}", ATTENTION_SOURCES, cuda=True, defines={"HEAD_DIM": d})
             lib.attn_decode_scratch_floats.restype = ctypes.c_size_t
+            lib.kernels_set_pdl(int(self.pdl))
             if lib.attn_head_dim() != d:
                 raise KernelError(f"attention library was built for head size {lib.attn_head_dim()}, wanted {d}")
             self._attn_libs[d] = lib
         return lib
 
-    def decode_splits(self, S: int, nkv: int, max_context: int) -> int:
-        """Splits of the key range per (request, key/value head) in a decode step: enough blocks
-        for two per SM, each with at least 256 keys, at most 32."""
+    def decode_splits(self, S: int, nkv: int, max_context: int, blocks_per_sm: int = 2) -> int:
+        """Splits of the key range per (request, key/value head) in a decode step.  Few requests:
+        as many splits as keep all blocks resident at once, at most 8 (every split costs an arrival
+        at the merge counter) and at least 256 keys each.  Many requests (more blocks than fit at
+        once): the smallest count up to 4 whose last wave is at least 85 % as full as the best
+        (the reference's heuristic has this shape, csrc/src/lib.rs:2122-2199)."""
         blocks = max(S * nkv, 1)
-        by_sm = -(-2 * self.num_sms // blocks)
-        by_len = max(1, max_context // 256)
-        return max(1, min(by_sm, by_len, 32))
+        capacity = self.num_sms * max(blocks_per_sm, 1)
+        most = max(1, max_context // 256)
+        if blocks < capacity:
+            return max(1, min(8, most, capacity // blocks))
+
+        def efficiency(s):
+            waves = blocks * s / capacity
+            return waves / -(-blocks * s // capacity)
+
+        most = min(most, 4)
+        best = max(efficiency(s) for s in range(1, most + 1))
+        return next(s for s in range(1, most + 1) if efficiency(s) >= 0.85 * best)
 
     def sample(self, logits, temperature, top_k, top_p, seed, step, out, num_rows=None):
         R, V = logits.shape

@@ -75,7 +75,7 @@ class StepFunction:
         # captured per padded batch size; the reference has no graphs.
         self.cuda_graphs = cuda_graphs and torch.cuda.is_available() and getattr(model, "graph_safe", True)
         self.max_model_len = max_model_len
-        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}
         self.graph_replays = 0
 
     # ------------------------------------------------------------------ metadata
@@ -191,11 +191,16 @@ class StepFunction:
     def _run_graph(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         S = len(entries)
         bucket = next(b for b in self.GRAPH_BUCKETS if b >= S)
-        g = self._graphs.get(bucket)
+        # Kernels size their work splits by the longest context; graphs are kept per power-of-two
+        # bound on it, so a captured split count stays right while contexts grow.
+        longest = max((self.manager.num_tokens(e.req) if self.manager.has_request(e.req) else 0) for e in entries) + 1
+        ctx_bound = max(256, 1 << (longest - 1).bit_length())
+        key = (bucket, ctx_bound)
+        g = self._graphs.get(key)
         if g is None:
             cap_stride = -(-max(self.max_model_len, 1) // self.page_size)
             cap = MetaLayout(bucket, bucket, bucket, (cap_stride,) * len(self.manager.groups)).size
-            g = self._graphs[bucket] = _DecodeGraph(torch.zeros(cap, dtype=torch.int32, device=self.rt.device), cap_stride)
+            g = self._graphs[key] = _DecodeGraph(torch.zeros(cap, dtype=torch.int32, device=self.rt.device), cap_stride)
         host, lay, infos, R = self.prepare(entries, pad_to=bucket)
         if max(lay.strides, default=0) > g.cap_stride:
             raise RuntimeError(f"a request holds more pages than max_model_len ({self.max_model_len}) allows")
@@ -203,7 +208,7 @@ class StepFunction:
         if g.graph is None:
             ctx = self.context(g.meta, lay, [])
             # sizes that pick kernels and splits are those of the bucket, not of this batch
-            ctx.decode_only, ctx.max_tokens_per_entry, ctx.max_context = True, 1, max(self.max_model_len, 1)
+            ctx.decode_only, ctx.max_tokens_per_entry, ctx.max_context = True, 1, ctx_bound
             rows = g.meta[lay.rows:lay.rows + bucket]
             if not g.warm:  # the first step of a bucket runs eagerly: libraries load, attributes get set
                 logits = self.model.forward(ctx, self.cache, rows, bucket)

@@ -74,11 +74,19 @@ class Attention(Mixer):
     def forward(self, x, ctx, cache):
         ops = self.rt.ops
         qkv = ops.linear(x, self.w_qkv, meta=ctx.meta)
-        self.position.encode_and_store(qkv, ctx, cache, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
-                                       head_dim=self.head_dim)
+        # In a decode step the attention kernel can rotate q and write the new key and value itself.
+        rope = None
+        fast = getattr(ops, "fast_attention", None)
+        if ctx.decode_only and getattr(ops, "fused_rope", True) and fast and fast(qkv.dtype, self.head_dim, self.num_heads, self.num_kv_heads, qkv.shape[1]):
+            rotary = self.position.rotary()
+            if rotary is not None:
+                rope = (rotary[0], rotary[1], cache.writes and cache.pages is not None)
+        if rope is None:
+            self.position.encode_and_store(qkv, ctx, cache, num_heads=self.num_heads, num_kv_heads=self.num_kv_heads,
+                                           head_dim=self.head_dim)
         out = torch.empty((ctx.T, self.q_size), dtype=x.dtype, device=x.device)
         ops.attention(qkv, qkv.shape[1], cache.pages, ctx, cache.group, out, self.num_heads, self.num_kv_heads,
-                      self.head_dim, cache.page_size, cache.num_pages, int(self.window or 0), self.scale)
+                      self.head_dim, cache.page_size, cache.num_pages, int(self.window or 0), self.scale, rope=rope)
         return ops.linear(out, self.w_o, meta=ctx.meta)
 
 

@@ -100,6 +100,11 @@ class PositionEncoding(Part):
                          num_kv_heads: int, head_dim: int) -> None:
         raise NotImplementedError
 
+    def rotary(self):
+        """(inv_freq on the device, rotary_dim) if the encoding is a rotation by position times
+        frequency, which the decode attention kernel can apply itself; None otherwise."""
+        return None
+
 
 class Mixer(Part):
     """Mixes information between the tokens of a request."""

@@ -53,6 +53,9 @@ class RotaryEncoding(PositionEncoding):
         super().bind(tensors, rt)
         self.inv_freq = self._frequencies().to(rt.device).contiguous()
 
+    def rotary(self):
+        return self.inv_freq, self.rotary_dim
+
     def encode_and_store(self, qkv, ctx, cache, *, num_heads, num_kv_heads, head_dim):
         self.rt.ops.rope_kv_store(qkv, ctx.positions, ctx.token_entry, ctx.meta, max(cache.group, 0), self.inv_freq,
                                   cache.pages, cache.num_pages, ctx.T, num_heads, num_kv_heads, head_dim,

@@ -90,6 +90,8 @@ def main() -> int:
                     help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points")
+    ap.add_argument("--phase", default="all", choices=["all", "prefill", "decode"],
+                    help="measure only one phase (for profiling); the JSON line then lacks the other")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -144,13 +146,13 @@ def main() -> int:
     # ------------------------------------------------------------------ prefill of 2,048 tokens
     toks = prompt()
     times = []
-    for i in range(3 + 5):
+    for i in range(3 + 5 if args.phase != "decode" else 0):
         req = 10 ** 6 + i
         ms = event_ms(lambda: lm.step.run([StepEntry(req, toks, [PREFILL_TOKENS - 1])]))
         lm.step.finish(req)
         if i >= 3:
             times.append(ms)
-    prefill_ms = statistics.median(times)
+    prefill_ms = statistics.median(times) if times else float("nan")
     prefill_flops = 2 * PREFILL_TOKENS * lin_params + 4 * (PREFILL_TOKENS ** 2 // 2) * d * nq * L + 2 * V * H
     prefill = {"value": PREFILL_TOKENS / prefill_ms * 1e3, "tokens": PREFILL_TOKENS, "ms": prefill_ms,
                "frac": prefill_flops / (prefill_ms * 1e-3) / (bf16_tflops * 1e12), "peak": f"{peak_kind} bf16 burst"}
@@ -183,6 +185,9 @@ def main() -> int:
             eng.abort_request(i)
         return ms, launches, ctx_mid
 
+    if args.phase == "prefill":
+        print(json.dumps({"impl": "ours", "phase": "prefill", "prefill": prefill}))
+        return 0
     clocks = ClockSampler()
     clocks.start()
     ms, launches, ctx_mid = decode_run(args.batch, args.steps, args.warmup, through_engine=False)
@@ -191,11 +196,13 @@ def main() -> int:
     value = args.batch * args.steps / ms * 1e3
     step_bytes = weight_bytes + args.batch * ctx_mid * kv_bytes_per_token
     achieved = step_bytes / (ms_step * 1e-3) / 1e9
-    e2e_ms, _, _ = decode_run(args.batch, args.steps, args.warmup, through_engine=True)
+    e2e_ms = float("nan")
+    if args.phase == "all":
+        e2e_ms, _, _ = decode_run(args.batch, args.steps, args.warmup, through_engine=True)
     meta_ints = 20 + 3 * args.batch + (args.batch + 1) + 2 * args.batch + args.batch \
         + args.batch * (-(-(PROMPT_LEN + DECODE_TOKENS) // PAGE))
     points = {}
-    if not args.skip_points:
+    if not args.skip_points and args.phase == "all":
         for b in (1, 64):
             pms, _, _ = decode_run(b, 32, 3, through_engine=False)
             points[f"decode_b{b}"] = b * 32 / pms * 1e3

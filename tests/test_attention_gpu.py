@@ -126,3 +126,48 @@ def test_head_sizes_beyond_the_kernels_are_refused(rts):
 
     with pytest.raises(KernelError):
         run_attention(rts["bfloat16"], [(0, 4)], 1, 1, 272, 16)
+
+
+@pytest.mark.parametrize("d,rot,nq,nkv,page,splits", [(64, 64, 32, 8, 16, 3), (64, 64, 3, 1, 8, 1), (128, 64, 8, 2, 16, 2),
+                                                       (16, 16, 4, 2, 4, 4)])
+def test_decode_with_fused_rotation_and_cache_write(rts, d, rot, nq, nkv, page, splits):
+    """The decode kernel given unrotated q, k, v of the new token: it must rotate q, write the rotated
+    key and the value to the right page and slot, and attend over old keys and the new one."""
+    rt = rts["bfloat16"]
+    contexts = [0, 1, 15, 16, 31, 32, 200, 513]
+    g = torch.Generator().manual_seed(d + splits)
+    lengths = [c + 1 for c in contexts]
+    tables, num_pages = K.scrambled_tables(lengths, page, d)
+    inv = torch.tensor([1.0 / 10000.0 ** (i / rot) for i in range(0, rot, 2)], dtype=torch.float32)
+    bf = lambda t: t.bfloat16().float()  # noqa: E731
+    qs = [bf(torch.randn(L, nq, d, generator=g)) for L in lengths]
+    ks = [bf(torch.randn(L, nkv, d, generator=g)) for L in lengths]
+    vs = [bf(torch.randn(L, nkv, d, generator=g)) for L in lengths]
+
+    def rotate(x):  # [L, heads, d] -> rotated in the first `rot` dims, rounded as the kernels round
+        y = x.clone().double()
+        y[..., :rot] = P.rope(x[..., :rot].double(), torch.arange(x.shape[0]), inv)
+        return bf(y.float())
+
+    rks, rqs = [rotate(k) for k in ks], [rotate(q) for q in qs]
+    cache = torch.full((num_pages, 2, nkv, page, d), float("nan"), dtype=torch.bfloat16, device=rt.device)
+    K.fill_cache(cache, tables, [rk[:-1] for rk in rks], [v[:-1] for v in vs], page)  # everything but the new token
+    ctx, _ = K.make_context(rt, [(c, 1) for c in contexts], page, tables)
+    S = len(contexts)
+    qkv = torch.zeros(S, (nq + 2 * nkv) * d, dtype=torch.bfloat16, device=rt.device)
+    for i in range(S):
+        qkv[i] = torch.cat([qs[i][-1].reshape(-1), ks[i][-1].reshape(-1), vs[i][-1].reshape(-1)]).bfloat16()
+    out = torch.full((S, nq * d), float("nan"), dtype=torch.bfloat16, device=rt.device)
+    rt.ops.decode_splits = lambda *a: splits
+    try:
+        rt.ops.attention(qkv, qkv.shape[1], cache, ctx, 0, out, nq, nkv, d, page, num_pages, 0, 1 / math.sqrt(d),
+                         rope=(inv.to(rt.device), rot, True))
+    finally:
+        del rt.ops.decode_splits
+    rt.ops.check_status()
+    for i, c in enumerate(contexts):
+        want = P.causal_attention(rqs[i].double(), rks[i].double(), vs[i].double(), 1 / math.sqrt(d))[-1]
+        assert (out[i].float().cpu().reshape(nq, d) - want.float()).abs().max() < 2e-2, c
+        pg, slot = tables[i][c // page], c % page
+        assert (cache[pg, 0, :, slot].float().cpu() - rks[i][-1]).abs().max() < 2e-2
+        assert torch.equal(cache[pg, 1, :, slot].float().cpu(), vs[i][-1])

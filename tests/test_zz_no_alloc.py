@@ -78,6 +78,6 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
         assert torch.equal(got, want)                            # and in fact the same bits
     # too large for the built-in array: refused, nothing launched, the message names the sizes
     rc = lib.attn_decode_noalloc(qkv.data_ptr(), qkv.shape[1], cache.data_ptr(), ctx.meta.data_ptr(), 0,
-                                 ctx.cu_tokens.data_ptr(), ctx.positions.data_ptr(), got.data_ptr(), 4096, nq, nkv, page,
+                                 ctx.cu_tokens.data_ptr(), ctx.positions.data_ptr(), got.data_ptr(), 2048, nq, nkv, page,
                                  num_pages, 0, scale, 32, ctx.max_context, rt.ops.status.data_ptr(), stream, err, 512)
     assert rc == -1 and b"floats of scratch" in err.value and b"1048576" in err.value
