@@ -510,9 +510,10 @@ attn_decode_kernel(bf16* __restrict__ q, int q_stride, bf16* __restrict__ cache,
 
 // ----------------------------------------------------------------------------- prefill (and mixed steps)
 namespace {
-constexpr int PF_KT = 64;    // keys per tile
+constexpr int PF_KT = 64;                 // keys per tile
 constexpr int PF_NK = PF_KT / 8;
-constexpr int PF_ROWS = 64;  // (token, head) rows per block: 4 warps x 16
+constexpr int PF_MT = 1;  // m16 tiles per warp (two halve the fragment loads but cost half the resident warps: measured slower)
+constexpr int PF_ROWS = 4 * 16 * PF_MT;   // (token, head) rows per block: 4 warps
 constexpr int PF_STAGES = 2;
 constexpr size_t PF_SMEM = (size_t)(PF_ROWS * LDS + PF_STAGES * 2 * PF_KT * LDS) * sizeof(bf16);
 }  // namespace
@@ -566,27 +567,40 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     };
     load_tile(0, 0);
     cp_async_commit();
-    const bf16* qwarp = qtile + warp * 16 * LDS;
-    uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
+    const int wrow = warp * 16 * PF_MT;  // first row of this warp
+    const bf16* qwarp = qtile + wrow * LDS;
+    uint32_t qf[PF_MT][Q_IN_REGS ? KSTEPS : 1][4];
     if (Q_IN_REGS) {
 #pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) load_a_frag(qf[ks], qwarp, ks, lane);
-    }
-    // positions of this thread's two rows (-1: a padding row, sees nothing)
-    int prow[2];
+        for (int mt = 0; mt < PF_MT; ++mt)
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        int tok = (warp * 16 + (lane >> 2) + 8 * h) / G;
-        prow[h] = tok < nt ? p_first + tok : -1;
+            for (int ks = 0; ks < KSTEPS; ++ks) load_a_frag(qf[mt][ks], qwarp + mt * 16 * LDS, ks, lane);
     }
-    const int warp_first_tok = (warp * 16) / G, warp_last_tok = min(nt - 1, (warp * 16 + 15) / G);
+    // positions of this thread's rows (-1: a padding row, sees nothing)
+    int prow[PF_MT][2];
+#pragma unroll
+    for (int mt = 0; mt < PF_MT; ++mt)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            int tok = (wrow + mt * 16 + (lane >> 2) + 8 * h) / G;
+            prow[mt][h] = tok < nt ? p_first + tok : -1;
+        }
+    const int warp_first_tok = wrow / G, warp_last_tok_all = (wrow + 16 * PF_MT - 1) / G;
+    const int warp_last_tok = min(nt - 1, warp_last_tok_all);
     const int warp_pmax = warp_first_tok < nt ? p_first + warp_last_tok : -1;
+    const int warp_pmin = p_first + warp_first_tok;
     const int warp_kmin = window > 0 ? max(0, p_first + warp_first_tok - window + 1) : 0;
+    const bool has_padding = warp_last_tok_all >= nt;
 
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    float o[DTILES][4];
+    float m[PF_MT][2], l[PF_MT][2];
+    float o[PF_MT][DTILES][4];
 #pragma unroll
-    for (int dt = 0; dt < DTILES; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+    for (int mt = 0; mt < PF_MT; ++mt) {
+        m[mt][0] = m[mt][1] = -INFINITY;
+        l[mt][0] = l[mt][1] = 0.f;
+#pragma unroll
+        for (int dt = 0; dt < DTILES; ++dt) o[mt][dt][0] = o[mt][dt][1] = o[mt][dt][2] = o[mt][dt][3] = 0.f;
+    }
 
     for (int t = 0; t < ntiles; ++t) {
         const int stage = t & 1;
@@ -602,35 +616,91 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
         if (k0 <= warp_pmax && k0 + PF_KT > warp_kmin) {  // the tile holds keys some row of this warp sees
             const bf16* ktile = kv + stage * 2 * PF_KT * LDS;
             const bf16* vtile = ktile + PF_KT * LDS;
-            float s[PF_NK][4];
-            qk_tile<PF_NK>(s, qf, qwarp, ktile, lane);
+            float s[PF_MT][PF_NK][4];
 #pragma unroll
-            for (int n = 0; n < PF_NK; ++n)
+            for (int mt = 0; mt < PF_MT; ++mt)
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    int key = k0 + n * 8 + (lane & 3) * 2 + (c & 1);
-                    int p = prow[c >> 1];
-                    bool vis = key <= p && (window <= 0 || p - key < window);
-                    s[n][c] = vis ? s[n][c] * scale_log2 : -INFINITY;
+                for (int n = 0; n < PF_NK; ++n) s[mt][n][0] = s[mt][n][1] = s[mt][n][2] = s[mt][n][3] = 0.f;
+            // S = Q K^T: a key fragment is loaded once and multiplied into every m-tile of the warp
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) {
+                uint32_t a[PF_MT][4];
+#pragma unroll
+                for (int mt = 0; mt < PF_MT; ++mt) {
+                    if (Q_IN_REGS) { a[mt][0] = qf[mt][ks][0]; a[mt][1] = qf[mt][ks][1]; a[mt][2] = qf[mt][ks][2]; a[mt][3] = qf[mt][ks][3]; }
+                    else load_a_frag(a[mt], qwarp + mt * 16 * LDS, ks, lane);
                 }
-            softmax_tile<PF_NK>(s, m, l, o);
-            pv_tile<PF_NK>(o, s, vtile, lane);
+#pragma unroll
+                for (int np = 0; np < PF_NK / 2; ++np) {
+                    uint32_t b[4];
+                    int j = lane >> 3;
+                    ldmatrix_x4(b, ktile + toff(np * 16 + (lane & 7) + (j >> 1) * 8, ks * 16 + (j & 1) * 8));
+#pragma unroll
+                    for (int mt = 0; mt < PF_MT; ++mt) {
+                        mma_bf16(s[mt][2 * np], a[mt], b[0], b[1]);
+                        mma_bf16(s[mt][2 * np + 1], a[mt], b[2], b[3]);
+                    }
+                }
+            }
+            // only tiles that cross a row's last visible key (or a window's edge, or the range's ends) need a mask
+            const bool need_mask = has_padding || window > 0 || k0 + PF_KT - 1 > warp_pmin || k0 < kbeg;
+#pragma unroll
+            for (int mt = 0; mt < PF_MT; ++mt) {
+#pragma unroll
+                for (int n = 0; n < PF_NK; ++n)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        bool vis = true;
+                        if (need_mask) {
+                            int key = k0 + n * 8 + (lane & 3) * 2 + (c & 1);
+                            int p = prow[mt][c >> 1];
+                            vis = key <= p && (window <= 0 || p - key < window);
+                        }
+                        s[mt][n][c] = vis ? s[mt][n][c] * scale_log2 : -INFINITY;
+                    }
+                softmax_tile<PF_NK>(s[mt], m[mt], l[mt], o[mt]);
+            }
+            // O += P V: a value fragment likewise serves every m-tile
+#pragma unroll
+            for (int ks = 0; ks < PF_NK / 2; ++ks) {
+                uint32_t a[PF_MT][4];
+#pragma unroll
+                for (int mt = 0; mt < PF_MT; ++mt) {
+                    a[mt][0] = pack_bf16(s[mt][2 * ks][0], s[mt][2 * ks][1]);
+                    a[mt][1] = pack_bf16(s[mt][2 * ks][2], s[mt][2 * ks][3]);
+                    a[mt][2] = pack_bf16(s[mt][2 * ks + 1][0], s[mt][2 * ks + 1][1]);
+                    a[mt][3] = pack_bf16(s[mt][2 * ks + 1][2], s[mt][2 * ks + 1][3]);
+                }
+#pragma unroll
+                for (int dp = 0; dp < DTILES / 2; ++dp) {
+                    uint32_t b[4];
+                    int j = lane >> 3;
+                    ldmatrix_x4_trans(b, vtile + toff(ks * 16 + (lane & 7) + (j & 1) * 8, dp * 16 + (j >> 1) * 8));
+#pragma unroll
+                    for (int mt = 0; mt < PF_MT; ++mt) {
+                        mma_bf16(o[mt][2 * dp], a[mt], b[0], b[1]);
+                        mma_bf16(o[mt][2 * dp + 1], a[mt], b[2], b[3]);
+                    }
+                }
+            }
         }
         __syncthreads();  // the stage may be overwritten by the load of the tile after next
     }
     const int g = lane >> 2, tig = lane & 3;
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        int r = warp * 16 + g + 8 * h;
-        int tok = r / G, hd = r % G;
-        if (tok >= nt) continue;
-        float inv = l[h] > 0.f ? 1.f / l[h] : 0.f;
-        bf16* orow = out + ((size_t)(row0 + t0 + tok) * nq + kvh * G + hd) * D;
+    for (int mt = 0; mt < PF_MT; ++mt)
 #pragma unroll
-        for (int dt = 0; dt < DTILES; ++dt)
-            *reinterpret_cast<__nv_bfloat162*>(orow + dt * 8 + tig * 2) =
-                __floats2bfloat162_rn(o[dt][2 * h] * inv, o[dt][2 * h + 1] * inv);
-    }
+        for (int h = 0; h < 2; ++h) {
+            int r = wrow + mt * 16 + g + 8 * h;
+            int tok = r / G, hd = r % G;
+            if (tok >= nt) continue;
+            float inv = l[mt][h] > 0.f ? 1.f / l[mt][h] : 0.f;
+            bf16* orow = out + ((size_t)(row0 + t0 + tok) * nq + kvh * G + hd) * D;
+#pragma unroll
+            for (int dt = 0; dt < DTILES; ++dt)
+                *reinterpret_cast<__nv_bfloat162*>(orow + dt * 8 + tig * 2) =
+                    __floats2bfloat162_rn(o[mt][dt][2 * h] * inv, o[mt][dt][2 * h + 1] * inv);
+        }
 }
 
 // ----------------------------------------------------------------------------- host side
@@ -648,7 +718,7 @@ extern "C" int attn_prefill(const void* q, int q_stride, const void* cache, cons
                             int page_size, int num_pages, int window, float scale, int max_context, int* status,
                             cudaStream_t stream) {
     if (S <= 0 || max_q_len <= 0) return 0;
-    if (nq % nkv || nq / nkv > PF_ROWS) return (int)cudaErrorInvalidValue;
+    if (nq % nkv || nq / nkv > 16) return (int)cudaErrorInvalidValue;
     CacheLayout L{nkv, page_size, D};
     int tpt = PF_ROWS / (nq / nkv);
     dim3 grid((max_q_len + tpt - 1) / tpt, nkv, S);

@@ -199,15 +199,15 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int* __restrict_
                                      const int* __restrict__ token_entry, const int* __restrict__ meta, int group,
                                      const float* __restrict__ inv_freq, T* __restrict__ cache, CacheLayout L,
                                      int nq, int rot, int store_kv, int num_pages, int* __restrict__ status) {
-    // one block per (token, head of the fused row): q heads, then k heads, then v heads
+    // one row of threads (threadIdx.y) per (token, head of the fused row): q heads, then k heads, then v heads
     pdl_launch_dependents();
     const int d = L.head_dim, nkv = L.num_kv_heads, half = rot / 2;
-    const int t = blockIdx.x, h = blockIdx.y;
+    const int t = blockIdx.x, h = blockIdx.y * blockDim.y + threadIdx.y;
     const bool is_q = h < nq, is_k = !is_q && h < nq + nkv;
     float freq = 0.f;
-    if (!(!is_q && !is_k) && (int)threadIdx.x < half) freq = inv_freq[threadIdx.x];  // a constant: before the wait
+    if ((is_q || is_k) && (int)threadIdx.x < half) freq = inv_freq[threadIdx.x];  // a constant: before the wait
     pdl_wait();
-    if (t >= meta[META_NUM_TOKENS]) return;
+    if (h >= nq + 2 * nkv || t >= meta[META_NUM_TOKENS]) return;
     if (!is_q && !store_kv) return;
     const int pos = positions[t];
     T* x = qkv + ((size_t)t * (nq + 2 * nkv) + h) * d;
@@ -242,8 +242,10 @@ extern "C" int rope_kv_store(void* qkv, int dtype, const int* positions, const i
                              int d, int rot, int page_size, int store_kv, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
     CacheLayout L{nkv, page_size, d};
-    int threads = d >= 128 ? 64 : 32;
-    dim3 grid(T, nq + 2 * nkv);
+    // few tokens: one head per block (many small blocks, short latency); many tokens: eight heads per block
+    int heads = nq + 2 * nkv, hpb = T >= 64 ? 8 : 1;
+    dim3 threads(d >= 128 ? 64 : 32, hpb);
+    dim3 grid(T, (heads + hpb - 1) / hpb);
     if (dtype == DT_F32)
         return (int)launch_kernel(rope_kv_store_kernel<float>, grid, threads, 0, stream, (float*)qkv, positions, token_entry,
                                   meta, group, inv_freq, (float*)cache, L, nq, rot, store_kv, num_pages, status);
@@ -380,15 +382,34 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, c
     pdl_wait();
     int t = blockIdx.y;
     if (t >= meta[META_NUM_TOKENS]) return;
-    int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= I) return;
-    float g = to_float(gu[(size_t)t * 2 * I + i]), u = to_float(gu[(size_t)t * 2 * I + I + i]);
-    out[(size_t)t * I + i] = from_float<T>(g / (1.f + expf(-g)) * u);
+    constexpr int V = 16 / sizeof(T);  // elements of a 16-byte access
+    const T* g = gu + (size_t)t * 2 * I;
+    T* o = out + (size_t)t * I;
+    int i = (blockIdx.x * blockDim.x + threadIdx.x) * V;
+    if (I % V == 0) {  // rows stay 16-byte aligned
+        if (i >= I) return;
+        uint4 gv = *reinterpret_cast<const uint4*>(g + i), uv = *reinterpret_cast<const uint4*>(g + I + i), ov;
+        const T* gp = reinterpret_cast<const T*>(&gv);
+        const T* up = reinterpret_cast<const T*>(&uv);
+        T* op = reinterpret_cast<T*>(&ov);
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+            float x = to_float(gp[j]);
+            op[j] = from_float<T>(x / (1.f + expf(-x)) * to_float(up[j]));
+        }
+        *reinterpret_cast<uint4*>(o + i) = ov;
+    } else {
+        for (int j = i; j < min(i + V, I); ++j) {
+            float x = to_float(g[j]);
+            o[j] = from_float<T>(x / (1.f + expf(-x)) * to_float(g[I + j]));
+        }
+    }
 }
 
 extern "C" int silu_mul(const void* gu, void* out, int dtype, const int* meta, int T, int I, cudaStream_t stream) {
     if (T <= 0) return 0;
-    dim3 grid((I + 255) / 256, T);
+    int per_block = 256 * (dtype == DT_F32 ? 4 : 8);
+    dim3 grid((I + per_block - 1) / per_block, T);
     if (dtype == DT_F32) return (int)launch_kernel(silu_mul_kernel<float>, grid, 256, 0, stream, (const float*)gu, (float*)out, meta, I);
     return (int)launch_kernel(silu_mul_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
                               meta, I);
