@@ -25,6 +25,7 @@ SKINNY_MAX_ROWS = 16  # bfloat16 linears with at most this many rows stream the 
 
 CORE_SOURCES = ["kernels/core.cu", "kernels/linear_bf16.cu", "kernels/sampling.cu"]
 ATTENTION_SOURCES = ["kernels/attention_bf16.cu"]
+GEMM_SOURCES = ["kernels/gemm_tcgen05.cu"]
 ATTENTION_HEAD_DIMS = (16, 64, 128)  # built by the build check; other head sizes are built when a model needs them
 
 
@@ -55,6 +56,7 @@ class CudaOps:
         self.status = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=self.device)
         self.launches = 0  # own kernel launches, counted for the benchmark record
         self._attn_libs = {}
+        self._gemm_lib = None
         self._counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # split arrivals; kernels leave zeros
         # Programmatic dependent launch lets a kernel start while its predecessor drains.  Measured on
         # the decode step of Llama 3.2 1B it made the step slower (1.17 ms against 0.97 ms), so it is
@@ -86,7 +88,8 @@ class CudaOps:
             self.status.zero_()
             raise KernelError(
                 f"device status: token id out of range at token {s[0] - 1}" if s[0] else
-                f"device status: block table names no valid page for token {s[1] - 1}"
+                f"device status: block table names no valid page for token {s[1] - 1}" if s[1] else
+                f"device status: a tensor-core GEMM block ({s[2] - 1}) gave up waiting on a barrier"
             )
 
     # ------------------------------------------------------------------ kernels
@@ -132,6 +135,22 @@ class CudaOps:
             self.silu_mul(y, out, meta, M, n_out)
             return out
         return y
+
+    def gemm_tc(self, a, b, *, out_dtype=None, silu_mul: bool = False, transpose: bool = False, bn: int = 256):
+        """C = A * B^T on tcgen05/TMEM with TMA-fed tiles (kernels/gemm_tcgen05.cu).  a [RA, K] fills the
+        128-row side of the MMA, b [RB, K] the BN-column side.  ``transpose``: the result is [RB, RA]
+        (used with a = weights when the activations have few rows).  ``silu_mul``: b is [gate; up]
+        stacked and the result has RB/2 columns."""
+        if self._gemm_lib is None:
+            self._gemm_lib = build.load_library("gemm_tcgen05", GEMM_SOURCES, cuda=True)
+        out_dtype = out_dtype or a.dtype
+        ra, K = a.shape
+        rb = b.shape[0] // 2 if silu_mul else b.shape[0]
+        shape = (rb, ra) if transpose else (ra, rb)
+        c = torch.empty(shape, dtype=out_dtype, device=a.device)
+        self._check(self._gemm_lib.gemm_tcgen05(_p(a), _p(b), _p(c), ra, rb, K, shape[1], _code(c), int(silu_mul),
+                                                int(transpose), bn, _p(self.status), self._stream()), "gemm_tcgen05")
+        return c
 
     def silu_mul(self, gu, out, meta, T: int, inter: int):
         self._check(self.lib.silu_mul(_p(gu), _p(out), _code(gu), _p(meta), T, inter, self._stream()), "silu_mul")

@@ -56,6 +56,15 @@ class _Request:
     def tokens(self) -> List[int]:
         return self.prompt + self.output
 
+    def token_span(self, start: int, n: int) -> List[int]:
+        """Tokens start .. start+n-1 of prompt + output, without building the whole list."""
+        p = len(self.prompt)
+        if start >= p:
+            return self.output[start - p:start - p + n]
+        if start + n <= p:
+            return self.prompt[start:start + n]
+        return self.prompt[start:] + self.output[:start + n - p]
+
 
 class Engine:
     def __init__(self, model_dir: str, config: Optional[EngineConfig] = None, **overrides):
@@ -131,7 +140,7 @@ class Engine:
             r = self._requests[e.req]
             if r.metrics.first_scheduled_time is None:
                 r.metrics.first_scheduled_time = now
-            toks = r.tokens[e.context_len:e.context_len + e.num_tokens]
+            toks = r.token_span(e.context_len, e.num_tokens)
             entries.append(StepEntry(e.req, toks, [e.num_tokens - 1] if e.samples else []))
             if e.samples:
                 sampled.append(r)
@@ -140,7 +149,7 @@ class Engine:
         self.num_steps += 1
         if sampled:
             tokens = self.sampler.sample(logits, [r.params for r in sampled], [len(r.output) for r in sampled],
-                                         [r.tokens for r in sampled])
+                                         [r.tokens if r.params.repetition_penalty != 1.0 else () for r in sampled])
             now = time.time()
             for r, tok in zip(sampled, tokens):
                 r.output.append(tok)

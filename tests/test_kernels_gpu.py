@@ -203,3 +203,31 @@ def test_repetition_penalty_kernel(rts):
     row = torch.tensor([1.0, 3.0, 3.0, -2.0, 0.5, 0.0], device=rt.device)
     rt.ops.repeat_penalty(row, 2.0, torch.tensor([1, 1, 3, 5, 1], dtype=torch.int32, device=rt.device))
     assert row.tolist() == P.apply_repeat_penalty(torch.tensor([1.0, 3.0, 3.0, -2.0, 0.5, 0.0]), 2.0, [1, 1, 3, 5, 1]).tolist()
+
+
+@pytest.mark.parametrize("ra,rb,K,kw", [
+    (128, 256, 64, dict(bn=256)),
+    (300, 1000, 200, dict(bn=128)),                       # ragged rows, columns and K (zero-filled by TMA)
+    (515, 777, 2048, dict(bn=256)),
+    (260, 320, 192, dict(bn=256, silu_mul=True)),         # SwiGLU epilogue on a stacked [gate; up] weight
+    (200, 1000, 264, dict(bn=256, out_dtype=torch.float32)),
+    (3072, 40, 2048, dict(bn=64, transpose=True)),        # weights fill the 128-row side, few activation rows
+    (1000, 17, 8192, dict(bn=32, transpose=True)),
+    (1000, 100, 264, dict(bn=128, transpose=True, out_dtype=torch.float32)),
+])
+def test_tcgen05_gemm(rts, ra, rb, K, kw):
+    """The TMA + tcgen05 + TMEM GEMM against a float64 product."""
+    rt = rts["bfloat16"]
+    g = torch.Generator().manual_seed(ra + rb)
+    a = torch.randn(ra, K, generator=g).bfloat16()
+    b = (torch.randn(rb * (2 if kw.get("silu_mul") else 1), K, generator=g) / math.sqrt(K)).bfloat16()
+    c = rt.ops.gemm_tc(a.to(rt.device), b.to(rt.device), **kw)
+    rt.ops.check_status()
+    ref = a.double() @ b.double().T
+    if kw.get("silu_mul"):
+        ref = ref[:, :rb] * torch.sigmoid(ref[:, :rb]) * ref[:, rb:]
+    if kw.get("transpose"):
+        ref = ref.T
+    assert c.shape == ref.shape
+    tol = 2e-5 if c.dtype == torch.float32 else 1e-2
+    assert (c.double().cpu() - ref).abs().max() < tol * max(1.0, float(ref.abs().max()))
