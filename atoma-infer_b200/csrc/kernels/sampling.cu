@@ -45,7 +45,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restrict__ temperature,
                    const int* __restrict__ top_k, const float* __restrict__ top_p,
                    const unsigned long long* __restrict__ seed, const unsigned long long* __restrict__ step,
-                   int* __restrict__ out, const int* __restrict__ num_rows) {
+                   int* __restrict__ out, const int* __restrict__ num_rows, const int* __restrict__ slots,
+                   int* __restrict__ last_tokens) {
     __shared__ float red[33];
     __shared__ float fsum[SAMPLE_THREADS];
     __shared__ ArgMax amax[32];
@@ -80,7 +81,11 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
     __syncthreads();
     best = amax[0];
     if (!(T > 0.f)) {
-        if (tid == 0) out[r] = best.i == 0x7fffffff ? 0 : best.i;
+        if (tid == 0) {
+            int tok = best.i == 0x7fffffff ? 0 : best.i;
+            out[r] = tok;
+            if (slots) last_tokens[slots[r]] = tok;  // where the next step's embedding can find it
+        }
         return;
     }
     const float m = best.v / T;
@@ -153,15 +158,19 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
         }
     }
     __syncthreads();
-    if (tid == 0) out[r] = found < V ? found : max(last_kept, 0);
+    if (tid == 0) {
+        int tok = found < V ? found : max(last_kept, 0);
+        out[r] = tok;
+        if (slots) last_tokens[slots[r]] = tok;
+    }
 }
 
 extern "C" int sample_rows(const float* logits, int R, int V, const float* temperature, const int* top_k,
                            const float* top_p, const unsigned long long* seed, const unsigned long long* step,
-                           int* out, const int* num_rows, cudaStream_t stream) {
+                           int* out, const int* num_rows, const int* slots, int* last_tokens, cudaStream_t stream) {
     if (R <= 0) return 0;
     return (int)launch_kernel(sample_rows_kernel, R, SAMPLE_THREADS, 0, stream, logits, V, temperature, top_k, top_p, seed,
-                              step, out, num_rows);
+                              step, out, num_rows, slots, last_tokens);
 }
 
 // Repetition penalty on one row: every distinct token id of `context` once; a

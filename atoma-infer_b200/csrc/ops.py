@@ -57,6 +57,7 @@ class CudaOps:
         self.launches = 0  # own kernel launches, counted for the benchmark record
         self._attn_libs = {}
         self._gemm_lib = None
+        self.last_tokens = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # by state slot
         self._counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # split arrivals; kernels leave zeros
         # Programmatic dependent launch lets a kernel start while its predecessor drains.  Measured on
         # the decode step of Llama 3.2 1B it made the step slower (1.17 ms against 0.97 ms), so it is
@@ -94,9 +95,10 @@ class CudaOps:
 
     # ------------------------------------------------------------------ kernels
     def embed(self, tokens, table, resid, meta, T: int):
+        """A token id -1 - s means: the token last sampled into slot s (``self.last_tokens``)."""
         H, V = table.shape[1], table.shape[0]
         self._check(self.lib.embed_rows(_p(tokens), _p(table), _code(table), _p(resid), _p(meta), T, H, V,
-                                        _p(self.status), self._stream()), "embed_rows")
+                                        _p(self.last_tokens), _p(self.status), self._stream()), "embed_rows")
 
     def add_rmsnorm(self, resid, delta, w, eps: float, out, meta, n: int, rows=None):
         """resid += delta (if given); out = rmsnorm(resid) * w.  With ``rows`` the sum and the
@@ -236,10 +238,12 @@ class CudaOps:
         best = max(efficiency(s) for s in range(1, most + 1))
         return next(s for s in range(1, most + 1) if efficiency(s) >= 0.85 * best)
 
-    def sample(self, logits, temperature, top_k, top_p, seed, step, out, num_rows=None):
+    def sample(self, logits, temperature, top_k, top_p, seed, step, out, num_rows=None, slots=None):
+        """``slots`` (int32 per row): also leave each token in ``self.last_tokens[slot]`` for the next step."""
         R, V = logits.shape
         self._check(self.lib.sample_rows(_p(logits), R, V, _p(temperature), _p(top_k), _p(top_p), _p(seed), _p(step),
-                                         _p(out), _p(num_rows), self._stream()), "sample_rows")
+                                         _p(out), _p(num_rows), _p(slots), _p(self.last_tokens), self._stream()),
+                    "sample_rows")
 
     def repeat_penalty(self, row, penalty: float, context):
         self._check(self.lib.repeat_penalty(_p(row), row.numel(), ctypes.c_float(penalty), _p(context),

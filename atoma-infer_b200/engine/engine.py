@@ -51,6 +51,8 @@ class _Request:
     params: ResolvedParams
     metrics: RequestMetrics
     output: List[int] = field(default_factory=list)
+    pending: int = 0             # tokens sampled on the device that the host has not read yet
+    ends_by_count: bool = False  # the token in flight is the request's last, whatever it is
 
     @property
     def tokens(self) -> List[int]:
@@ -87,6 +89,7 @@ class Engine:
         self.sampler = Sampler(self.lm.rt)
         self.eos_token_ids = tuple(spec.eos_token_ids)
         self._requests: Dict[int, _Request] = {}
+        self._inflight = None  # (requests sampled, their tokens on the way to the host, event) of the last step
         self._next_id = 0
         self.num_steps = 0
         self.num_generated = 0
@@ -119,11 +122,21 @@ class Engine:
             del self._requests[req]
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_unfinished()
+        return self.scheduler.has_unfinished() or self._inflight is not None
 
     # ------------------------------------------------------------------ one step
     def step(self) -> List[RequestOutput]:
-        """Plans and runs one step; returns the requests that ended in it."""
+        """Plans and launches one step, then reads the tokens of the step before it; returns the
+        requests that ended.
+
+        The host runs one step ahead of the device: a decode step is launched with "the token
+        last sampled for this request" left on the device by the sampler, so the device never
+        waits for the host to read tokens, plan and build the next step.  Stop rules that need
+        the token's value (end-of-sequence, stop ids) therefore act one step late; the extra
+        token such a request computes meanwhile is dropped.  Rules that only count (max_new_tokens,
+        the model length) act at once.  Requests with a repetition penalty need their history on
+        the host, so steps that sample for one are read back before the next is launched.
+        """
         plan = self.scheduler.schedule()
         now = time.time()
         finished: List[RequestOutput] = []
@@ -134,36 +147,80 @@ class Engine:
         for req in plan.preempted:
             self._requests[req].metrics.num_preemptions += 1
         if not plan.entries:
+            finished += self._resolve()
             return finished
-        entries, sampled = [], []
+        # a portion that needs the value of a token still on the device (a request sent back to
+        # prefill right after sampling): read the tokens first
         for e in plan.entries:
             r = self._requests[e.req]
+            known = len(r.prompt) + len(r.output)
+            if r.pending and e.context_len + e.num_tokens > known and not (e.num_tokens == 1 and e.context_len == known):
+                finished += self._resolve()
+                break
+        entries, sampled = [], []
+        for e in plan.entries:
+            r = self._requests.get(e.req)
+            if r is None:  # ended while the tokens were read just above
+                continue
             if r.metrics.first_scheduled_time is None:
                 r.metrics.first_scheduled_time = now
-            toks = r.token_span(e.context_len, e.num_tokens)
+            if r.pending and e.num_tokens == 1 and e.context_len == len(r.prompt) + len(r.output):
+                toks = [-1 - self.lm.manager.state_slot(e.req)]  # the token the sampler left on the device
+            else:
+                toks = r.token_span(e.context_len, e.num_tokens)
             entries.append(StepEntry(e.req, toks, [e.num_tokens - 1] if e.samples else []))
             if e.samples:
                 sampled.append(r)
+        if not entries:
+            self.scheduler.step_done()
+            return finished
         logits = self.lm.step.run(entries)
         self.scheduler.step_done()
         self.num_steps += 1
+        previous, self._inflight = self._inflight, None
         if sampled:
-            tokens = self.sampler.sample(logits, [r.params for r in sampled], [len(r.output) for r in sampled],
-                                         [r.tokens if r.params.repetition_penalty != 1.0 else () for r in sampled])
-            now = time.time()
-            for r, tok in zip(sampled, tokens):
-                r.output.append(tok)
-                self.num_generated += 1
-                if r.metrics.first_token_time is None:
-                    r.metrics.first_token_time = now
-                reason = self._stop_reason(r, tok)
-                if reason:
-                    self.scheduler.finish(r.req)
-                    r.metrics.finished_time = now
-                    del self._requests[r.req]
-                    finished.append(RequestOutput(r.req, r.prompt, r.output, reason, r.metrics))
+            slots = [self.lm.manager.state_slot(r.req) for r in sampled]
+            tokens, event = self.sampler.sample(
+                logits, [r.params for r in sampled], [len(r.output) + r.pending for r in sampled],
+                [r.tokens if r.params.repetition_penalty != 1.0 else () for r in sampled], slots=slots, defer=True)
+            for r in sampled:
+                r.pending += 1
+                n_out = len(r.output) + r.pending
+                p = r.params
+                if len(r.prompt) + n_out >= self.max_model_len or (p.max_new_tokens is not None and n_out >= p.max_new_tokens):
+                    r.ends_by_count = True       # whatever the token is, the request ends with it
                 else:
                     self.scheduler.append_token(r.req)
+            self._inflight = (sampled, tokens, event)
+        finished += self._resolve(previous)
+        if self._inflight and any(r.params.repetition_penalty != 1.0 for r in self._inflight[0]):
+            finished += self._resolve()
+        return finished
+
+    def _resolve(self, inflight="current") -> List[RequestOutput]:
+        """Reads the tokens of a launched step (waits for them if need be) and applies the stop rules."""
+        if inflight == "current":
+            inflight, self._inflight = self._inflight, None
+        if not inflight:
+            return []
+        sampled, tokens, event = inflight
+        event.synchronize()
+        now = time.time()
+        finished = []
+        for r, tok in zip(sampled, tokens.tolist()):
+            if self._requests.get(r.req) is not r:
+                continue  # ended or aborted since: its extra token is dropped
+            r.pending -= 1
+            r.output.append(tok)
+            self.num_generated += 1
+            if r.metrics.first_token_time is None:
+                r.metrics.first_token_time = now
+            reason = self._stop_reason(r, tok)
+            if reason:
+                self.scheduler.finish(r.req)
+                r.metrics.finished_time = now
+                del self._requests[r.req]
+                finished.append(RequestOutput(r.req, r.prompt, r.output, reason, r.metrics))
         return finished
 
     def _stop_reason(self, r: _Request, tok: int) -> Optional[str]:
@@ -189,9 +246,6 @@ class Engine:
         ids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
         done: Dict[int, RequestOutput] = {}
         while self.has_unfinished():
-            outs = self.step()
-            for o in outs:
+            for o in self.step():
                 done[o.request_id] = o
-            if not outs and not self.has_unfinished():
-                break
         return [done[i] for i in ids]

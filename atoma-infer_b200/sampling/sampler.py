@@ -22,12 +22,15 @@ class Sampler:
         self._pinned = torch.cuda.is_available()
 
     def sample(self, logits: torch.Tensor, params: Sequence[ResolvedParams], steps: Sequence[int],
-               histories: Sequence[Sequence[int]]) -> List[int]:
+               histories: Sequence[Sequence[int]], slots: Sequence[int] = (), defer: bool = False):
         """``logits`` [R, vocab] float32 on the device; ``steps[i]``: how many tokens request i
-        has sampled before; ``histories[i]``: its tokens so far (for the repetition penalty)."""
+        has sampled before; ``histories[i]``: its tokens so far (for the repetition penalty);
+        ``slots[i]``: where to leave the token on the device for the next step's embedding.
+        Returns the token ids as a list, or with ``defer`` as a pinned host tensor whose copy is
+        still in flight together with the CUDA event that marks its arrival."""
         R = logits.shape[0]
         if R == 0:
-            return []
+            return ([], None) if defer else []
         ops, dev = self.rt.ops, self.rt.device
         for i, p in enumerate(params):
             if p.repetition_penalty != 1.0:
@@ -36,8 +39,11 @@ class Sampler:
                     ops.repeat_penalty(logits[i], p.repetition_penalty,
                                        torch.tensor(ctx, dtype=torch.int32).to(dev, non_blocking=True))
         # one buffer: seed u64 | step u64 | temperature f32 | top_k i32 | top_p f32 (64-bit arrays first: aligned)
-        host = torch.empty(7 * R, dtype=torch.int32, pin_memory=self._pinned)
+        S = R if len(slots) else 0
+        host = torch.empty(7 * R + S, dtype=torch.int32, pin_memory=self._pinned)
         h = host.numpy()
+        if S:
+            h[7 * R:8 * R] = list(slots)
         h[0:2 * R].view(np.uint64)[:] = [p.seed for p in params]
         h[2 * R:4 * R].view(np.uint64)[:] = list(steps)
         h[4 * R:5 * R].view(np.float32)[:] = [0.0 if p.greedy else p.temperature for p in params]
@@ -46,5 +52,11 @@ class Sampler:
         d = host.to(dev, non_blocking=True)
         out = torch.empty(R, dtype=torch.int32, device=dev)
         ops.sample(logits, d[4 * R:5 * R].view(torch.float32), d[5 * R:6 * R], d[6 * R:7 * R].view(torch.float32),
-                   d[0:2 * R], d[2 * R:4 * R], out)
-        return out.tolist()
+                   d[0:2 * R], d[2 * R:4 * R], out, slots=d[7 * R:8 * R] if S else None)
+        if not defer:
+            return out.tolist()
+        back = torch.empty(R, dtype=torch.int32, pin_memory=self._pinned)
+        back.copy_(out, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return back, event
