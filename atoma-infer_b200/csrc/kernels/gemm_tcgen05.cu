@@ -21,12 +21,15 @@
 // Every wait on an mbarrier is bounded: when the bound is hit the kernel raises a status word,
 // stops issuing work, releases its tensor memory and returns (a wrong result, reported, instead
 // of a hang).
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "common.cuh"
 
 int g_use_pdl = 0;
 extern "C" void kernels_set_pdl(int on) { g_use_pdl = on ? 1 : 0; }
+
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -135,7 +138,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int tile_a = blockIdx.x, tile_b = blockIdx.y;
     const int a0 = tile_a * BM;
     const int b0 = tile_b * (EPI == 1 ? BN / 2 : BN);  // first output column (row of B) of the tile
-    const int num_kb = (K + BK - 1) / BK;
+    // K may be split over the blocks of a thread-block cluster (gridDim.z of them): each takes a range
+    // of 64-wide k blocks and the partial tiles are added through distributed shared memory.
+    const int ksplit = gridDim.z;
+    const int kb_all = (K + BK - 1) / BK, kb_per = (kb_all + ksplit - 1) / ksplit;
+    const int kb_first = blockIdx.z * kb_per;
+    const int num_kb = max(0, min(kb_all, kb_first + kb_per) - kb_first);
 
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -162,12 +170,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             unsigned char* a_dst = tiles + s * STAGE_BYTES;
             unsigned char* b_dst = a_dst + A_BYTES;
             mbar_expect_tx(&full_bar[s], STAGE_BYTES);
-            tma_load_2d(a_dst, &map_a, kb * BK, a0, &full_bar[s]);
+            tma_load_2d(a_dst, &map_a, (kb_first + kb) * BK, a0, &full_bar[s]);
             if (EPI == 1) {
-                tma_load_2d(b_dst, &map_b, kb * BK, b0, &full_bar[s]);               // gate rows
-                tma_load_2d(b_dst + B_BYTES / 2, &map_b2, kb * BK, b0, &full_bar[s]);  // up rows
+                tma_load_2d(b_dst, &map_b, (kb_first + kb) * BK, b0, &full_bar[s]);               // gate rows
+                tma_load_2d(b_dst + B_BYTES / 2, &map_b2, (kb_first + kb) * BK, b0, &full_bar[s]);  // up rows
             } else {
-                tma_load_2d(b_dst, &map_b, kb * BK, b0, &full_bar[s]);
+                tma_load_2d(b_dst, &map_b, (kb_first + kb) * BK, b0, &full_bar[s]);
             }
             armed = kb + 1;
         }
@@ -201,7 +209,36 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     // ---- epilogue: warp w owns TMEM lanes 32w .. 32w+31 = rows a0 + 32w + lane of the tile
     bool ready = mbar_wait(accum_bar, 0, status, abort_flag);
     tc_fence_after();
-    if (ready && !*abort_flag) {
+    if (ksplit > 1) {
+        // Partial tile -> this block's shared memory (the stages are idle now), then every block of
+        // the cluster adds up a band of rows over all ranks, in rank order, and stores it.
+        float* part = reinterpret_cast<float*>(tiles);  // [128][BN]
+        if (ready && !*abort_flag) {
+            const bool any = num_kb > 0;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                if (any) tmem_ld16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) part[(warp * 32 + lane) * BN + c0 + i] = any ? v[i] : 0.f;
+            }
+        }
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        const int band = (BM + ksplit - 1) / ksplit, r_lo = blockIdx.z * band, r_hi = min(BM, r_lo + band);
+        for (int idx = tid; idx < (r_hi - r_lo) * BN; idx += 128) {
+            // consecutive threads take consecutive rows of A: in the transposed store they are neighbours in memory
+            int r = r_lo + idx % (r_hi - r_lo), j = idx / (r_hi - r_lo);
+            float v = 0.f;
+            for (int rank = 0; rank < ksplit; ++rank) v += cluster.map_shared_rank(part, rank)[r * BN + j];
+            int ra = a0 + r, rb = b0 + j;
+            if (ra < rows_a && rb < rows_b) {
+                if (TRANS) c[(size_t)rb * ldc + ra] = from_float<TO>(v);
+                else c[(size_t)ra * ldc + rb] = from_float<TO>(v);
+            }
+        }
+        cluster.sync();  // nobody leaves while its partial tile may still be read
+    } else if (ready && !*abort_flag) {
         const int ra = a0 + warp * 32 + lane;
         constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;
 #pragma unroll 1
@@ -286,7 +323,8 @@ bool make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows)
 }
 
 template <int BN, typename TO, int EPI, bool TRANS>
-int launch(const void* a, const void* b, void* c, int rows_a, int rows_b, int K, int ldc, int* status, cudaStream_t stream) {
+int launch(const void* a, const void* b, void* c, int rows_a, int rows_b, int K, int ldc, int ksplit, int* status,
+           cudaStream_t stream) {
     constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
     constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
     constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 1) * 8 + 16 + 1024;
@@ -304,9 +342,21 @@ int launch(const void* a, const void* b, void* c, int rows_a, int rows_b, int K,
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid((rows_a + BM - 1) / BM, (rows_b + BOX_B - 1) / BOX_B);
-    kernel<<<grid, 128, SMEM, stream>>>(ma, mb, mb2, (TO*)c, rows_a, rows_b, K, ldc, status);
-    LAUNCH_RETURN();
+    if (EPI != 0 && ksplit != 1) return (int)cudaErrorInvalidValue;
+    if (ksplit < 1 || ksplit > 8 || (size_t)BM * BN * 4 > (size_t)STAGES * STAGE_BYTES) return (int)cudaErrorInvalidValue;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((rows_a + BM - 1) / BM, (rows_b + BOX_B - 1) / BOX_B, ksplit);
+    cfg.blockDim = dim3(128, 1, 1);
+    cfg.dynamicSmemBytes = SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = ksplit;
+    cfg.attrs = attr;
+    cfg.numAttrs = ksplit > 1 ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, ma, mb, mb2, (TO*)c, rows_a, rows_b, K, ldc, status);
 }
 
 }  // namespace
@@ -314,12 +364,13 @@ int launch(const void* a, const void* b, void* c, int rows_a, int rows_b, int K,
 // C = A * B^T.  a [rows_a, K], b [rows_b, K] (for epilogue 1: [2 * rows_b, K], gate rows then up rows),
 // bfloat16, K % 8 == 0, 16-byte aligned.  transpose = 0: c[rows_a, ldc] gets row ra, column rb;
 // transpose = 1: c[rows_b, ldc] gets row rb, column ra.  bn: columns of B per tile (32, 64, 128 or 256).
+// ksplit: blocks (of one cluster) that share a tile's K range, 1..8.
 extern "C" int gemm_tcgen05(const void* a, const void* b, void* c, int rows_a, int rows_b, int K, int ldc, int out_dtype,
-                            int epilogue, int transpose, int bn, int* status, cudaStream_t stream) {
+                            int epilogue, int transpose, int bn, int ksplit, int* status, cudaStream_t stream) {
     if (rows_a <= 0 || rows_b <= 0) return 0;
     if (K % 8 || K <= 0) return (int)cudaErrorInvalidValue;
     if (((uintptr_t)a | (uintptr_t)b) & 15) return (int)cudaErrorInvalidValue;
-#define GO(BN, TO, EPI, TR) return launch<BN, TO, EPI, TR>(a, b, c, rows_a, rows_b, K, ldc, status, stream)
+#define GO(BN, TO, EPI, TR) return launch<BN, TO, EPI, TR>(a, b, c, rows_a, rows_b, K, ldc, ksplit, status, stream)
     const bool f32 = out_dtype == DT_F32;
     if (!transpose) {
         if (epilogue == 1) {

@@ -138,11 +138,12 @@ class CudaOps:
             return out
         return y
 
-    def gemm_tc(self, a, b, *, out_dtype=None, silu_mul: bool = False, transpose: bool = False, bn: int = 256):
+    def gemm_tc(self, a, b, *, out_dtype=None, silu_mul: bool = False, transpose: bool = False, bn: int = 256,
+                ksplit: int = 1):
         """C = A * B^T on tcgen05/TMEM with TMA-fed tiles (kernels/gemm_tcgen05.cu).  a [RA, K] fills the
         128-row side of the MMA, b [RB, K] the BN-column side.  ``transpose``: the result is [RB, RA]
         (used with a = weights when the activations have few rows).  ``silu_mul``: b is [gate; up]
-        stacked and the result has RB/2 columns."""
+        stacked and the result has RB/2 columns.  ``ksplit``: blocks of a cluster that share a tile's K."""
         if self._gemm_lib is None:
             self._gemm_lib = build.load_library("gemm_tcgen05", GEMM_SOURCES, cuda=True)
         out_dtype = out_dtype or a.dtype
@@ -151,7 +152,8 @@ class CudaOps:
         shape = (rb, ra) if transpose else (ra, rb)
         c = torch.empty(shape, dtype=out_dtype, device=a.device)
         self._check(self._gemm_lib.gemm_tcgen05(_p(a), _p(b), _p(c), ra, rb, K, shape[1], _code(c), int(silu_mul),
-                                                int(transpose), bn, _p(self.status), self._stream()), "gemm_tcgen05")
+                                                int(transpose), bn, ksplit, _p(self.status), self._stream()),
+                    "gemm_tcgen05")
         return c
 
     def silu_mul(self, gu, out, meta, T: int, inter: int):
