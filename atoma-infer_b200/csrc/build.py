@@ -135,8 +135,10 @@ def host_library() -> ctypes.CDLL:
 
 def all_kernel_libraries():
     """(name, sources, defines) of every kernel library, for the build check."""
-    from .ops import ATTENTION_HEAD_DIMS, ATTENTION_SOURCES, CORE_SOURCES, GEMM_SOURCES
+    from .ops import (ATTENTION_HEAD_DIMS, ATTENTION_SOURCES, ATTENTION_TC_HEAD_DIMS, ATTENTION_TC_SOURCES, CORE_SOURCES,
+                      GEMM_SOURCES)
 
     return [("core", CORE_SOURCES, None), ("gemm_tcgen05", GEMM_SOURCES, None)] + [
         (f"attention_d{d}", ATTENTION_SOURCES, {"HEAD_DIM": d}) for d in ATTENTION_HEAD_DIMS] + [
-        ("attention_noalloc_d64", ["kernels/attention_noalloc.cu"], {"HEAD_DIM": 64})]
+        ("attention_noalloc_d64", ["kernels/attention_noalloc.cu"], {"HEAD_DIM": 64})] + [
+        (f"attention_tc_d{d}", ATTENTION_TC_SOURCES, {"HEAD_DIM": d}) for d in ATTENTION_TC_HEAD_DIMS]

@@ -26,6 +26,8 @@ SKINNY_MAX_ROWS = 16  # bfloat16 linears with at most this many rows stream the 
 CORE_SOURCES = ["kernels/core.cu", "kernels/linear_bf16.cu", "kernels/sampling.cu"]
 ATTENTION_SOURCES = ["kernels/attention_bf16.cu"]
 GEMM_SOURCES = ["kernels/gemm_tcgen05.cu"]
+ATTENTION_TC_SOURCES = ["kernels/attention_tcgen05.cu"]
+ATTENTION_TC_HEAD_DIMS = (64, 128)  # head sizes of the tcgen05 prefill attention
 ATTENTION_HEAD_DIMS = (16, 64, 128)  # built by the build check; other head sizes are built when a model needs them
 
 
@@ -56,6 +58,8 @@ class CudaOps:
         self.status = torch.zeros(STATUS_WORDS, dtype=torch.int32, device=self.device)
         self.launches = 0  # own kernel launches, counted for the benchmark record
         self._attn_libs = {}
+        self._attn_tc_libs = {}
+        self.tc_attention = os.environ.get("ATOMA_INFER_TC_ATTENTION", "1") != "0"  # tcgen05 prefill attention
         self._gemm_lib = None
         self.last_tokens = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # by state slot
         self._counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # split arrivals; kernels leave zeros
@@ -90,7 +94,8 @@ class CudaOps:
             raise KernelError(
                 f"device status: token id out of range at token {s[0] - 1}" if s[0] else
                 f"device status: block table names no valid page for token {s[1] - 1}" if s[1] else
-                f"device status: a tensor-core GEMM block ({s[2] - 1}) gave up waiting on a barrier"
+                f"device status: a tensor-core GEMM block ({s[2] - 1}) gave up waiting on a barrier" if s[2] else
+                f"device status: a tensor-core attention block ({s[3] - 1}) gave up waiting on a barrier"
             )
 
     # ------------------------------------------------------------------ kernels
@@ -196,6 +201,12 @@ class CudaOps:
                                             window, ctypes.c_float(scale), splits, ctx.max_context, _p(self.status),
                                             self._stream()),
                             "attn_decode")
+            elif self._prefill_tc(d, page_size, nq, nkv) is not None:
+                tc = self._prefill_tc(d, page_size, nq, nkv)
+                self._check(tc.attn_prefill_tc(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
+                                               _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
+                                               page_size, num_pages, window, ctypes.c_float(scale), ctx.max_context,
+                                               _p(self.status), self._stream()), "attn_prefill_tc")
             else:
                 self._check(lib.attn_prefill(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
                                              _p(ctx.context_lens), _p(out), S, ctx.max_tokens_per_entry, nq, nkv,
@@ -208,6 +219,18 @@ class CudaOps:
                                           _p(ctx.token_entry), _p(ctx.positions), _p(out), T, nq, nkv, d, page_size,
                                           num_pages, window, ctypes.c_float(scale), _p(self.status), self._stream()),
                     "attn_generic")
+
+    def _prefill_tc(self, d: int, page_size: int, nq: int, nkv: int):
+        """The tcgen05 prefill attention library for this geometry, or None (then the mma.sync kernel runs)."""
+        if d not in ATTENTION_TC_HEAD_DIMS or not self.tc_attention:
+            return None
+        lib = self._attn_tc_libs.get(d)
+        if lib is None:
+            lib = build.load_library(f"attention_tc_d{d}", ATTENTION_TC_SOURCES, cuda=True, defines={"HEAD_DIM": d})
+            if lib.attn_tc_head_dim() != d:
+                raise KernelError(f"tcgen05 attention library was built for head size {lib.attn_tc_head_dim()}, wanted {d}")
+            self._attn_tc_libs[d] = lib
+        return lib if lib.attn_prefill_tc_supports(page_size, nq, nkv) else None
 
     def _attention_library(self, d: int):
         lib = self._attn_libs.get(d)
