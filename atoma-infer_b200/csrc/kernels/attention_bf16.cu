@@ -529,7 +529,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     int* bt_s = reinterpret_cast<int*>(smem_raw + PF_SMEM);
     pdl_launch_dependents();
     pdl_wait();
-    const int qt = blockIdx.x, kvh = blockIdx.y, e = blockIdx.z;
+    // late query tiles see the most keys: they go first, so the longest blocks are not the last to start
+    const int qt = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y, e = blockIdx.z;
     if (e >= meta[META_NUM_ENTRIES]) return;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = nq / L.num_kv_heads;

@@ -136,17 +136,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* q_s = smem;
-    unsigned char* k_s = q_s + HALVES * HALF_BYTES;
-    unsigned char* v_s = k_s + HALVES * HALF_BYTES;
+    unsigned char* k_s = q_s + HALVES * HALF_BYTES;       // two stages
+    unsigned char* v_s = k_s + 2 * HALVES * HALF_BYTES;
     unsigned char* p_s = v_s + HALVES * HALF_BYTES;  // [2 key halves][128 rows x 64 keys]
     uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + 2 * HALF_BYTES);
-    uint64_t *k_full = bars, *v_full = bars + 1, *s_done = bars + 2, *o_done = bars + 3;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 4);
+    uint64_t *k_full = bars, *s_done = bars + 2, *v_full = bars + 4, *o_done = bars + 5;  // k_full[2], s_done[2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    float* row_max = reinterpret_cast<float*>(tmem_slot + 2);  // [2 halves][128 rows]
-    int* bt_s = reinterpret_cast<int*>(row_max + 2 * BQ);
+    float* row_max = reinterpret_cast<float*>(tmem_slot + 2);  // [2 sets][2 halves][128 rows]
+    int* bt_s = reinterpret_cast<int*>(row_max + 4 * BQ);
 
-    const int qt = blockIdx.x, kvh = blockIdx.y, e = blockIdx.z;
+    // late query tiles see the most keys: they go first, so the longest blocks are not the last to start
+    const int qt = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y, e = blockIdx.z;
     if (e >= meta[META_NUM_ENTRIES]) return;
     const int tid = threadIdx.x, warp = tid >> 5;
     const int row = tid & (BQ - 1), half = tid >> 7;  // my query row; my half of the keys and of the head
@@ -176,7 +177,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
         bt_s[i] = page;
     }
     if (tid == 0) {
-        mbar_init(k_full, 1); mbar_init(v_full, 1); mbar_init(s_done, 1); mbar_init(o_done, 1);
+        mbar_init(&k_full[0], 1); mbar_init(&k_full[1], 1); mbar_init(&s_done[0], 1); mbar_init(&s_done[1], 1);
+        mbar_init(v_full, 1); mbar_init(o_done, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -222,9 +224,29 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
                 tma_load_2d(dst + h * HALF_BYTES + pg * ps * 128, &map_kv, h * 64, r, bar);
         }
     };
+    // Tile t keeps its scores in tensor-memory buffer t & 1 (128 columns) and, once the softmax has read
+    // them, its P V product in the same columns; its keys sit in shared-memory stage t & 1.  So the
+    // tensor core computes the scores of tile t + 1 while the threads do the softmax of tile t.
+    constexpr int K_STAGE = HALVES * HALF_BYTES;
+    constexpr uint32_t idesc_s = make_idesc(BQ, BKV, false), idesc_o = make_idesc(BQ, D, true);
+    auto issue_scores = [&](int t) {  // by thread 0: S(t) = Q K(t)^T into buffer t & 1
+        const int b = t & 1;
+        if (mbar_wait(&k_full[b], (t >> 1) & 1, status, abort_flag)) {
+            tc_fence_after();
+#pragma unroll
+            for (int kd = 0; kd < D / 16; ++kd) {
+                uint32_t off = (kd / 4) * HALF_BYTES + (kd % 4) * 32;
+                umma_bf16(tmem_base + b * BKV, make_desc(smem_u32(q_s) + off, 0),
+                          make_desc(smem_u32(k_s) + b * K_STAGE + off, 0), idesc_s, kd > 0);
+            }
+        }
+        umma_commit(&s_done[b]);
+    };
     if (warp == 0) {
-        issue_loads(0, 0, k_s, k_full);
+        issue_loads(0, 0, k_s, &k_full[0]);
+        if (ntiles > 1) issue_loads(1, 0, k_s + K_STAGE, &k_full[1]);
         issue_loads(0, 1, v_s, v_full);
+        if (tid == 0) issue_scores(0);
     }
 
 #ifdef ATTN_TC_PROFILE
@@ -241,38 +263,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     float o[DH];
 #pragma unroll
     for (int i = 0; i < DH; ++i) o[i] = 0.f;
-    constexpr uint32_t idesc_s = make_idesc(BQ, BKV, false), idesc_o = make_idesc(BQ, D, true);
     bool ok = true;
 
     for (int t = 0; t < ntiles && ok; ++t) {
         const uint32_t ph = t & 1;
         const int k0 = k_first + t * BKV;
-        // ---- S = Q K^T
-        if (tid == 0) {
-            if (mbar_wait(k_full, ph, status, abort_flag)) {
-                tc_fence_after();
-#pragma unroll
-                for (int kd = 0; kd < D / 16; ++kd) {
-                    uint32_t off = (kd / 4) * HALF_BYTES + (kd % 4) * 32;
-                    umma_bf16(tmem_base, make_desc(smem_u32(q_s) + off, 0), make_desc(smem_u32(k_s) + off, 0), idesc_s, kd > 0);
-                }
-            }
-            umma_commit(s_done);
-        }
+        const int b = t & 1;
+        const uint32_t tmem_buf = tmem_row + b * BKV;
         PROF();
-        ok = mbar_wait(s_done, ph, status, abort_flag);
+        ok = mbar_wait(&s_done[b], (t >> 1) & 1, status, abort_flag);
         if (!ok) break;
         tc_fence_after();
         PROF();
-        if (warp == 0 && t + 1 < ntiles) issue_loads(t + 1, 0, k_s, k_full);  // K's buffer is free again
+        if (warp == 0 && t + 2 < ntiles) issue_loads(t + 2, 0, k_s + b * K_STAGE, &k_full[b]);  // this stage of K is free again
 
         // ---- softmax of my half row: the 64 scores stay in registers between the max and the exponentials
         const bool need_mask = window > 0 || k0 + BKV - 1 > p_first || k0 < kbeg || nt < TPT;  // same for the whole block
         float s[64];
         {
             float lo[32], hi[32];
-            tmem_ld32(tmem_row + half * 64, lo);
-            tmem_ld32(tmem_row + half * 64 + 32, hi);
+            tmem_ld32(tmem_buf + half * 64, lo);
+            tmem_ld32(tmem_buf + half * 64 + 32, hi);
 #pragma unroll
             for (int i = 0; i < 32; ++i) { s[i] = lo[i]; s[32 + i] = hi[i]; }  // unscaled: the scale goes into the exponent's FMA
         }
@@ -284,12 +295,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
                 s[i] = vis ? s[i] : -INFINITY;
             }
         }
+        // the row's maximum: the two threads of a row (warps w and w + 4) swap their halves' maxima through
+        // shared memory and meet at a barrier of their own, 64 threads wide, not the whole block's
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
         for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
-        row_max[half * BQ + row] = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-        __syncthreads();
-        const float mx = fmaxf(row_max[row], row_max[BQ + row]) * scale_log2;  // scale > 0: the max commutes with it
+        float* slot = row_max + (t & 1) * 2 * BQ;  // two sets, so that a fast pair cannot overwrite a slow reader's value
+        slot[half * BQ + row] = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+        asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");
+        const float mx = fmaxf(slot[row], slot[BQ + row]) * scale_log2;  // scale > 0: the max commutes with it
         const float m_new = fmaxf(m_run, mx);
         const float base = m_new == -INFINITY ? 0.f : m_new;
         const float corr = fast_exp2(m_run - base);
@@ -335,10 +349,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
 #pragma unroll
             for (int ks = 0; ks < BKV / 16; ++ks) {
                 uint64_t a = make_desc(smem_u32(p_s) + (ks / 4) * HALF_BYTES + (ks % 4) * 32, 0);
-                uint64_t b = make_desc(smem_u32(v_s) + ks * 16 * 128, HALF_BYTES);
-                umma_bf16(tmem_base + BKV, a, b, idesc_o, ks > 0);
+                uint64_t bd = make_desc(smem_u32(v_s) + ks * 16 * 128, HALF_BYTES);
+                umma_bf16(tmem_base + b * BKV, a, bd, idesc_o, ks > 0);  // over this tile's scores, which are consumed
             }
             umma_commit(o_done);
+            // The next tile's scores follow at once, into the other buffer: every thread has passed the
+            // barrier above, so it is done with that buffer (the product of the tile before this one).
+            if (t + 1 < ntiles) issue_scores(t + 1);
         }
         ok = mbar_wait(o_done, ph, status, abort_flag);
         if (!ok) break;
@@ -348,12 +365,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
 #pragma unroll
         for (int ch = 0; ch < DH / 32; ++ch) {
             float v[32];
-            tmem_ld32(tmem_row + BKV + half * DH + ch * 32, v);
+            tmem_ld32(tmem_buf + half * DH + ch * 32, v);
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[ch * 32 + i] = o[ch * 32 + i] * corr + v[i];
         }
-        tc_fence_before();
-        __syncthreads();  // every row has read S and O_tile before the next tile's MMAs overwrite them
+        tc_fence_before();  // the buffer is written again only after the next tile's barrier, which follows these reads
         PROF();
     }
 
@@ -377,7 +393,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     }
     if (!ok && tid == 0) {
         // gave up on a barrier: let copies that may still be in flight land (bounded) before the block leaves
-        for (uint32_t i = 0; i < WAIT_LIMIT && !(mbar_try_wait(k_full, 0) || mbar_try_wait(k_full, 1)); ++i) {}
+        for (uint32_t i = 0; i < WAIT_LIMIT && !(mbar_try_wait(&k_full[0], 0) || mbar_try_wait(&k_full[0], 1)); ++i) {}
+        for (uint32_t i = 0; i < WAIT_LIMIT && !(mbar_try_wait(&k_full[1], 0) || mbar_try_wait(&k_full[1], 1)); ++i) {}
         for (uint32_t i = 0; i < WAIT_LIMIT && !(mbar_try_wait(v_full, 0) || mbar_try_wait(v_full, 1)); ++i) {}
     }
     tc_fence_before();
@@ -401,7 +418,7 @@ EncodeTiledFn encode_fn() {
     }
     return fn;
 }
-constexpr size_t TC_SMEM_FIXED = (size_t)(3 * HALVES + 2) * HALF_BYTES + 4 * 8 + 16 + 2 * BQ * 4 + 1024;
+constexpr size_t TC_SMEM_FIXED = (size_t)(4 * HALVES + 2) * HALF_BYTES + 6 * 8 + 16 + 4 * BQ * 4 + 1024;
 }  // namespace
 
 extern "C" int attn_tc_head_dim() { return D; }
