@@ -24,7 +24,7 @@
 #define HEAD_DIM 64
 #endif
 int g_use_pdl = 1;
-extern "C" void kernels_set_pdl(int on) { g_use_pdl = on ? 1 : 0; }
+extern "C" void kernels_set_pdl(int mode) { g_use_pdl = mode; }
 
 static_assert(HEAD_DIM % 16 == 0 && HEAD_DIM >= 16 && HEAD_DIM <= 256, "head sizes 16..256 in steps of 16");
 

@@ -28,7 +28,7 @@
 static_assert(HEAD_DIM == 64 || HEAD_DIM == 128, "the tcgen05 attention kernel is built for head sizes 64 and 128");
 
 int g_use_pdl = 0;
-extern "C" void kernels_set_pdl(int on) { g_use_pdl = on ? 1 : 0; }
+extern "C" void kernels_set_pdl(int mode) { g_use_pdl = mode; }
 
 namespace {
 

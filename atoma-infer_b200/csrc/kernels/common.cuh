@@ -95,7 +95,7 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-extern int g_use_pdl;  // one per library (defined in its main file), set through kernels_set_pdl
+extern int g_use_pdl;  // per library, set through kernels_set_pdl: bit 0 all kernels, bit 1 only the large few-row linears
 
 template <typename... KArgs, typename... Args>
 static inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
@@ -109,6 +109,6 @@ static inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = g_use_pdl ? 1 : 0;
+    cfg.numAttrs = (g_use_pdl & 1) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }

@@ -13,7 +13,7 @@
 #include "common.cuh"
 
 int g_use_pdl = 1;
-extern "C" void kernels_set_pdl(int on) { g_use_pdl = on ? 1 : 0; }
+extern "C" void kernels_set_pdl(int mode) { g_use_pdl = mode; }
 
 // ----------------------------------------------------------------------------- embedding
 // resid[t, :] = table[tokens[t], :], widened to float32 (the residual stream is float32).

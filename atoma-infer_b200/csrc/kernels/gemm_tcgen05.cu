@@ -27,7 +27,7 @@
 #include "common.cuh"
 
 int g_use_pdl = 0;
-extern "C" void kernels_set_pdl(int on) { g_use_pdl = on ? 1 : 0; }
+extern "C" void kernels_set_pdl(int mode) { g_use_pdl = mode; }
 
 namespace cg = cooperative_groups;
 

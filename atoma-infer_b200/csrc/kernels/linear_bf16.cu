@@ -188,7 +188,7 @@ extern "C" int linear_skinny(const void* x, const void* w, void* y, int out_dtyp
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     // a cluster only when K is split; the dependent-launch attribute when it is switched on
     cfg.attrs = ksplits > 1 ? attr : attr + 1;
-    cfg.numAttrs = (ksplits > 1 ? 1 : 0) + (g_use_pdl ? 1 : 0);
+    cfg.numAttrs = (ksplits > 1 ? 1 : 0) + (((g_use_pdl & 1) || ((g_use_pdl & 2) && (size_t)N * K >= ((size_t)1 << 22))) ? 1 : 0);
     cudaError_t err;
 #define SMALL(TO, NT, EPI) err = cudaLaunchKernelEx(&cfg, linear_small_kernel<TO, NT, EPI>, xb, wb, (TO*)y, M, N, K, ksplits)
     if (epilogue == 1) {

@@ -63,10 +63,12 @@ class CudaOps:
         self._gemm_lib = None
         self.last_tokens = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # by state slot
         self._counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # split arrivals; kernels leave zeros
-        # Programmatic dependent launch lets a kernel start while its predecessor drains.  Measured on
-        # the decode step of Llama 3.2 1B it made the step slower (1.17 ms against 0.97 ms), so it is
-        # off unless ATOMA_INFER_PDL=1; ATOMA_INFER_FUSED_ROPE=0 switches the fused rotation off.
-        self.pdl = os.environ.get("ATOMA_INFER_PDL", "0") == "1"
+        # Programmatic dependent launch lets a kernel start while its predecessor drains (its weight
+        # loads are in flight before the dependency wait).  Measured on the decode step of Llama 3.2 1B:
+        # on for the few-row linears and the attention kernels 0.913 ms, off 0.967 ms, on for every
+        # kernel (norms included) 1.17 ms.  ATOMA_INFER_PDL: "0" off, "1" every kernel, default "linear".
+        mode = os.environ.get("ATOMA_INFER_PDL", "linear")
+        self.pdl = {"0": 0, "1": 1, "linear": 2}.get(mode, 2)
         self.fused_rope = os.environ.get("ATOMA_INFER_FUSED_ROPE", "1") != "0"
         self.lib.kernels_set_pdl(int(self.pdl))
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
@@ -81,10 +83,10 @@ class CudaOps:
             raise KernelError(f"{what}: CUDA error {err}")
 
     def set_pdl(self, on: bool) -> None:
-        self.pdl = bool(on)
+        self.pdl = int(on)
         self.lib.kernels_set_pdl(int(on))
         for lib in self._attn_libs.values():
-            lib.kernels_set_pdl(int(on))
+            lib.kernels_set_pdl(1 if on else 0)
 
     def check_status(self) -> None:
         """Raises if a kernel of an earlier launch met a bad token id or page id (synchronises)."""
@@ -237,7 +239,7 @@ class CudaOps:
         if lib is None:
             lib = build.load_library(f"attention_d{d}", ATTENTION_SOURCES, cuda=True, defines={"HEAD_DIM": d})
             lib.attn_decode_scratch_floats.restype = ctypes.c_size_t
-            lib.kernels_set_pdl(int(self.pdl))
+            lib.kernels_set_pdl(1 if self.pdl else 0)
             if lib.attn_head_dim() != d:
                 raise KernelError(f"attention library was built for head size {lib.attn_head_dim()}, wanted {d}")
             self._attn_libs[d] = lib
