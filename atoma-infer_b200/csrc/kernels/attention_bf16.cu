@@ -18,6 +18,10 @@
 // The reference does both with FlashAttention-2 for sm80 (csrc/kernels/flash_fwd_kernel.h:
 // compute_attn_1rowblock :56-500, compute_attn_1rowblock_splitkv :504-1092, combine
 // :1131-1313), one query head per block in the paged case (csrc/src/lib.rs:1576-1602).
+#include <cuda.h>
+
+#include <cstring>
+
 #include "common.cuh"
 
 #ifndef HEAD_DIM
@@ -42,6 +46,27 @@ constexpr bool Q_IN_REGS = D <= 128;  // larger heads reload Q fragments from sh
 constexpr float LOG2E = 1.4426950408889634f;
 
 typedef __nv_bfloat16 bf16;
+
+// ---- TMA page loads for the decode kernel (head size 64: a page's rows are exactly one 128-byte swizzle row)
+constexpr bool DEC_TMA = D == 64;
+constexpr uint32_t TMA_WAIT_LIMIT = 1u << 22;
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"((uint32_t)__cvta_generic_to_shared(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(map), "r"(x), "r"(y),
+                   "r"((uint32_t)__cvta_generic_to_shared(bar)) : "memory");
+}
 
 // element offset of (row, col) in a tile; vector accesses pass a col that is a multiple of 8
 __device__ __forceinline__ int toff(int row, int col) {
@@ -238,19 +263,28 @@ constexpr int DEC_BLOCKS_PER_SM = (int)((227 * 1024) / (DEC_SMEM + 1024)) < 8 ? 
 // Before the dependency wait the kernel only touches what no kernel of the step writes: the
 // step's metadata (block table, positions) and keys and values of earlier steps.
 __global__ void __launch_bounds__(DEC_WARPS * 32)
-attn_decode_kernel(bf16* __restrict__ q, int q_stride, bf16* __restrict__ cache, CacheLayout L,
+attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16* __restrict__ q, int q_stride,
+                   bf16* __restrict__ cache, CacheLayout L,
                    const int* __restrict__ meta, int group, const int* __restrict__ cu_tokens,
                    const int* __restrict__ positions, bf16* __restrict__ out, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int* __restrict__ counters, const float* __restrict__ inv_freq, int rot,
                    int store_kv, int nq, int window, float scale_log2, int num_pages, int splits,
                    int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    bf16* qtile = reinterpret_cast<bf16*>(smem_raw);
+    // tiles start on 1024-byte boundaries: TMA writes them with the 128-byte swizzle, whose pattern follows the address
+    unsigned char* smem_al = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    bf16* qtile = reinterpret_cast<bf16*>(smem_al);
     bf16* tiles = qtile + 16 * LDS;
     __shared__ int s_last;
+    __shared__ __align__(8) uint64_t tile_bar[DEC_WARPS][2];  // a warp's stage is full (TMA path)
     pdl_launch_dependents();
     const int split = blockIdx.x, kvh = blockIdx.y, e = blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const bool tma = DEC_TMA && use_tma;
+    if (tma && tid == 0) {
+        for (int w = 0; w < DEC_WARPS; ++w) { mbar_init(&tile_bar[w][0], 1); mbar_init(&tile_bar[w][1], 1); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     const bool live = e < meta[META_NUM_ENTRIES];
     const int G = nq / L.num_kv_heads;
     const int row0 = live ? cu_tokens[e] : 0;
@@ -278,6 +312,44 @@ attn_decode_kernel(bf16* __restrict__ q, int q_stride, bf16* __restrict__ cache,
     auto load_tile = [&](int t, int stage, const int (&pg)[RPL]) {
         bf16* ktile = mine + stage * 2 * DEC_KT * LDS;
         bf16* vtile = ktile + DEC_KT * LDS;
+        if (tma) {
+            // One box per page and per K|V instead of 16 sixteen-byte copies per lane.  Lane 0 holds the
+            // pages of tile rows 0, 8, 16, 24 in pg[0..3]; the page size is 8, 16 or 32 here.
+            const int k0 = lo + t * DEC_KT;
+            uint32_t bytes = 0;
+            bool okp[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                int pos0 = k0 + 8 * i;
+                okp[i] = i < RPL && (8 * i) % ps == 0 && pos0 < hi && pg[i < RPL ? i : 0] > 0 && pg[i < RPL ? i : 0] < num_pages;
+                if (okp[i]) bytes += (uint32_t)ps * 128u * 2u;
+                if (i < RPL && (8 * i) % ps == 0 && pos0 < hi && !okp[i] && lane == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + pos0);
+            }
+            // rows of pages that are not loaded: zeros (all lanes; a value row nobody wrote must not reach P*V)
+            for (int r = lane; r < DEC_KT; r += 32) {
+                if (!okp[(r / ps) * ps / 8]) {
+#pragma unroll
+                    for (int c = 0; c < D; c += 8) {
+                        *reinterpret_cast<uint4*>(ktile + toff(r, c)) = make_uint4(0u, 0u, 0u, 0u);
+                        *reinterpret_cast<uint4*>(vtile + toff(r, c)) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // this warp's reads and zero stores come before the copies
+            __syncwarp();
+            if (lane == 0) {
+                mbar_expect_tx(&tile_bar[warp][stage], bytes);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (!okp[i]) continue;
+                    int row_k = ((pg[i < RPL ? i : 0] * 2 + 0) * L.num_kv_heads + kvh) * ps;
+                    int row_v = ((pg[i < RPL ? i : 0] * 2 + 1) * L.num_kv_heads + kvh) * ps;
+                    tma_load_2d(ktile + 8 * i * LDS, &map_kv, 0, row_k, &tile_bar[warp][stage]);
+                    tma_load_2d(vtile + 8 * i * LDS, &map_kv, 0, row_v, &tile_bar[warp][stage]);
+                }
+            }
+            return;
+        }
 #pragma unroll
         for (int i = 0; i < RPL; ++i) {
             int idx = lane + 32 * i, r = idx / PAIRS, c = (idx % PAIRS) * 16;
@@ -362,6 +434,7 @@ attn_decode_kernel(bf16* __restrict__ q, int q_stride, bf16* __restrict__ cache,
                 for (int i = rot + tid; i < D; i += DEC_WARPS * 32) kd[i] = kx[i];
                 for (int i = tid; i < D; i += DEC_WARPS * 32) vd[i] = vx[i];
                 __threadfence();
+                asm volatile("fence.proxy.async.global;" ::: "memory");  // the page may be fetched by TMA next
             }
         }
     } else {
@@ -397,9 +470,26 @@ attn_decode_kernel(bf16* __restrict__ q, int q_stride, bf16* __restrict__ cache,
         } else {
             cp_async_wait<0>();
         }
+        bf16* ktile = mine + stage * 2 * DEC_KT * LDS;
+        bf16* vtile = ktile + DEC_KT * LDS;
+        if (tma) {
+            // the stage's it/2-th use: its barrier flips once per use (bounded wait)
+            const uint32_t parity = (uint32_t)(it >> 1) & 1u;
+            bool arrived = false;
+            for (uint32_t spin = 0; spin < TMA_WAIT_LIMIT && !arrived; ++spin) arrived = mbar_try_wait(&tile_bar[warp][stage], parity);
+            if (!arrived) {
+                if (lane == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + lo);
+                break;
+            }
+            // a page is copied whole: value rows beyond the split's last key are zeroed (0 * garbage must stay 0)
+            const int k0z = lo + t * DEC_KT;
+            if (k0z + DEC_KT > hi) {
+                for (int r = max(hi - k0z, 0) + lane; r < DEC_KT; r += 32)
+#pragma unroll
+                    for (int c = 0; c < D; c += 8) *reinterpret_cast<uint4*>(vtile + toff(r, c)) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
         __syncwarp();
-        const bf16* ktile = mine + stage * 2 * DEC_KT * LDS;
-        const bf16* vtile = ktile + DEC_KT * LDS;
         float s[DEC_NK][4];
         qk_tile<DEC_NK>(s, qf, qtile, ktile, lane);
         const int k0 = lo + t * DEC_KT;
@@ -705,6 +795,15 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
 }
 
 // ----------------------------------------------------------------------------- host side
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+int g_decode_tma = 1;
+}  // namespace
+// 0: the decode kernel loads pages with cp.async even where it could use TMA (for comparison).
+extern "C" void attn_set_decode_tma(int on) { g_decode_tma = on; }
+
 extern "C" int attn_head_dim() { return D; }
 // How many decode blocks fit a multiprocessor (by shared memory): the host sizes the splits by it.
 extern "C" int attn_decode_blocks_per_sm() { return DEC_BLOCKS_PER_SM; }
@@ -754,15 +853,39 @@ extern "C" int attn_decode(const void* q, int q_stride, const void* cache, const
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)S * nq * splits * D : nullptr;
     (void)max_context;
-    const size_t smem = DEC_SMEM;
+    const size_t smem = DEC_SMEM + 1024;  // room to start the tiles on a 1024-byte boundary
     static bool configured = false;  // once: the attribute is not set again inside a stream capture
     if (!configured) {
         cudaError_t err = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
         configured = true;
     }
+    // Page loads by TMA when a page's rows tile a warp's 32-key tile and start on its boundaries.
+    CUtensorMap map;
+    memset(&map, 0, sizeof map);
+    int use_tma = 0;
+    if (DEC_TMA && g_decode_tma && window <= 0 && (page_size == 8 || page_size == 16 || page_size == 32)) {
+        static EncodeTiledFn fn = nullptr;
+        if (!fn) {
+            void* p = nullptr;
+            cudaDriverEntryPointQueryResult qres;
+            if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+                qres == cudaDriverEntryPointSuccess)
+                fn = reinterpret_cast<EncodeTiledFn>(p);
+        }
+        if (fn) {
+            // the layer's cache as a matrix: one row per (page, K|V, head, slot), HEAD_DIM columns
+            cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_pages * 2 * nkv * page_size};
+            cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+            cuuint32_t box[2] = {(cuuint32_t)D, (cuuint32_t)page_size};
+            cuuint32_t estr[2] = {1, 1};
+            use_tma = fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+        }
+    }
     dim3 grid(splits, nkv, S);
-    return (int)launch_kernel(attn_decode_kernel, grid, DEC_WARPS * 32, smem, stream, (bf16*)q, q_stride, (bf16*)cache, L, meta,
+    return (int)launch_kernel(attn_decode_kernel, grid, DEC_WARPS * 32, smem, stream, map, use_tma, (bf16*)q, q_stride, (bf16*)cache, L, meta,
                               group, cu_tokens, positions, (bf16*)out, part_o, part_ml, counters, inv_freq, rot, store_kv, nq,
                               window, scale * LOG2E, num_pages, splits, status);
 }

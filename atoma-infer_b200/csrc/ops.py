@@ -240,6 +240,8 @@ class CudaOps:
             lib = build.load_library(f"attention_d{d}", ATTENTION_SOURCES, cuda=True, defines={"HEAD_DIM": d})
             lib.attn_decode_scratch_floats.restype = ctypes.c_size_t
             lib.kernels_set_pdl(1 if self.pdl else 0)
+            # page loads of the decode kernel by TMA: measured no faster than cp.async (13.1 vs 15.4 us at batch 8), so opt-in
+            lib.attn_set_decode_tma(int(os.environ.get("ATOMA_INFER_DECODE_TMA", "0") == "1"))
             if lib.attn_head_dim() != d:
                 raise KernelError(f"attention library was built for head size {lib.attn_head_dim()}, wanted {d}")
             self._attn_libs[d] = lib

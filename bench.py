@@ -114,7 +114,11 @@ def main() -> int:
 
     hbm_gbs, bf16_tflops, peak_kind = peaks()
     cfg = dict(MODEL, num_hidden_layers=args.layers)
+    import atexit
+    import shutil
+
     tmp = tempfile.mkdtemp(prefix="bench_model_")
+    atexit.register(shutil.rmtree, tmp, ignore_errors=True)  # 2.5 GB of random weights: do not leave them behind
     write_random_model(tmp, cfg, seed=0, std=0.02, device="cuda")
     L, H, I, V = args.layers, cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]

@@ -171,3 +171,18 @@ def test_decode_with_fused_rotation_and_cache_write(rts, d, rot, nq, nkv, page, 
         pg, slot = tables[i][c // page], c % page
         assert (cache[pg, 0, :, slot].float().cpu() - rks[i][-1]).abs().max() < 2e-2
         assert torch.equal(cache[pg, 1, :, slot].float().cpu(), vs[i][-1])
+
+
+def test_decode_page_loads_by_tma(rts):
+    """The decode kernel's TMA page loads (opt-in) give the same result as its cp.async loads."""
+    lib = rts["bfloat16"].ops._attention_library(64)
+    entries = [(0, 1), (15, 1), (16, 1), (31, 1), (300, 1), (777, 1), (1023, 1)]
+    try:
+        lib.attn_set_decode_tma(1)
+        for page, splits in ((16, 1), (16, 5), (8, 3), (32, 2)):
+            got, want = run_attention(rts["bfloat16"], entries, 32, 8, 64, page, seed=splits, splits=splits)
+            assert worst(got, want) < 2e-2, (page, splits)
+        got, want = run_attention(rts["bfloat16"], [(599, 1)], 4, 2, 64, 16, seed=255, stand_out=255, scale=1.0, splits=4)
+        assert worst(got, want) < 3e-2
+    finally:
+        lib.attn_set_decode_tma(0)
