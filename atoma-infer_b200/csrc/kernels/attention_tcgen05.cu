@@ -188,7 +188,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     }
     // my half of my query row, swizzled, straight into the A-operand tile
     const int my_tok = row / G, my_hd = row % G;
-    const bool my_valid = my_tok < nt;
+    const bool my_valid = my_tok < nt && row < TPT * G;  // group sizes that do not divide 128 leave padding rows
     const int my_pos = my_valid ? p_first + my_tok : -1;
     {
         const bf16* src = q + (size_t)(row0 + t0 + my_tok) * q_stride + (size_t)(kvh * G + my_hd) * D;
@@ -426,7 +426,7 @@ extern "C" int attn_tc_head_dim() { return D; }
 // Page sizes this kernel takes: one TMA box per page, boxes that tile a 128-key tile and start on a swizzle atom.
 extern "C" int attn_prefill_tc_supports(int page_size, int nq, int nkv) {
     bool ps_ok = page_size >= 8 && page_size <= 128 && (page_size & (page_size - 1)) == 0;
-    return ps_ok && nq % nkv == 0 && BQ % (nq / nkv) == 0;
+    return ps_ok && nq % nkv == 0 && nq / nkv <= 16;
 }
 
 extern "C" int attn_prefill_tc(const void* q, int q_stride, const void* cache, const int* meta, int group,

@@ -21,6 +21,6 @@ def tiny_models(tmp_path_factory):
     out = {}
     for name, (cfg, page) in helpers.TINY.items():
         d = str(tmp_path_factory.mktemp(f"tiny{name}"))
-        helpers.make_model(d, cfg, seed=1 if name == "B" else 0)
+        helpers.make_model(d, cfg, seed={"A": 0, "B": 1, "C": 2}[name])
         out[name] = (d, cfg, page)
     return out

@@ -35,7 +35,16 @@ CONFIG_B = {
                      "original_max_position_embeddings": 64, "rope_type": "llama3"},
     "max_position_embeddings": 1024, "tie_word_embeddings": False, "eos_token_id": [998, 999],
 }
-TINY = {"A": (CONFIG_A, 4), "B": (CONFIG_B, 8)}  # name -> (config, page size)
+# C: the head size (128) and group size (3 query heads per key/value head) of the larger Llama 3 models, page 16
+CONFIG_C = {
+    "architectures": ["LlamaForCausalLM"], "hidden_size": 768, "intermediate_size": 1024, "vocab_size": 777,
+    "num_hidden_layers": 2, "num_attention_heads": 6, "num_key_value_heads": 2, "rms_norm_eps": 1e-5,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 128, "rope_type": "llama3"},
+    "max_position_embeddings": 2048, "tie_word_embeddings": False, "eos_token_id": 776,
+}
+TINY = {"A": (CONFIG_A, 4), "B": (CONFIG_B, 8), "C": (CONFIG_C, 16)}  # name -> (config, page size)
 
 FP32_TOL = 2e-5   # times the largest |logit| of the sequence
 BF16_TOL = 3e-2

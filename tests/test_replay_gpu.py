@@ -7,7 +7,7 @@ import plain_llama as P
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": (1, 7, 16, 33, 70, 131), "B": (5, 29, 64, 97, 150)}
+LENGTHS = {"A": (1, 7, 16, 33, 70, 131), "B": (5, 29, 64, 97, 150), "C": (3, 40, 129, 300)}
 
 
 @pytest.fixture(scope="module")
@@ -21,7 +21,7 @@ def references(tiny_models):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_every_cutting_matches_plain(name, dtype, tiny_models, references, tmp_path):
     d, cfg, page = tiny_models[name]
     seqs, ref = references[name]
