@@ -12,17 +12,21 @@
 //  * attn_decode: one block per (split, key/value head, request) for steps in which
 //    every request brings one token.  The group's query heads are the rows of one
 //    m16 tile, each key byte is read once; the four warps walk different key tiles
-//    (more loads in flight) and merge at the end; with several splits the partial
-//    results go to scratch memory and attn_combine merges them.
+//    (more loads in flight) and merge at the end; several splits of a key range are a
+//    thread-block cluster that merges through distributed shared memory (or, beyond the
+//    cluster size, through scratch memory, merged by whichever block arrives last).
 //
 // The reference does both with FlashAttention-2 for sm80 (csrc/kernels/flash_fwd_kernel.h:
 // compute_attn_1rowblock :56-500, compute_attn_1rowblock_splitkv :504-1092, combine
 // :1131-1313), one query head per block in the paged case (csrc/src/lib.rs:1576-1602).
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include <cstring>
 
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 #ifndef HEAD_DIM
 #define HEAD_DIM 64
@@ -247,8 +251,11 @@ constexpr int DEC_STAGES = D <= 128 ? 2 : 1;
 constexpr int DEC_WARP_ELEMS = DEC_STAGES * 2 * DEC_KT * LDS;  // bf16 elements of one warp's K/V stages
 constexpr size_t DEC_TILE_BYTES = (size_t)(16 * LDS + DEC_WARPS * DEC_WARP_ELEMS) * sizeof(bf16);
 constexpr size_t DEC_MERGE_BYTES = (size_t)DEC_WARPS * (32 + 16 * D) * sizeof(float);
-constexpr size_t DEC_SMEM = 16 * LDS * sizeof(bf16) +
+constexpr size_t DEC_MAIN_BYTES = 16 * LDS * sizeof(bf16) +
     (DEC_WARPS * DEC_WARP_ELEMS * sizeof(bf16) > DEC_MERGE_BYTES ? DEC_WARPS * DEC_WARP_ELEMS * sizeof(bf16) : DEC_MERGE_BYTES);
+constexpr int DEC_MAX_CLUSTER = 8;                     // splits that can merge through the cluster's shared memory
+constexpr size_t DEC_SHARE_BYTES = (size_t)(16 * D + 32) * sizeof(float);  // a block's result for its cluster: o[16][D], (m, l)[16]
+constexpr size_t DEC_SMEM = DEC_MAIN_BYTES + DEC_SHARE_BYTES;
 constexpr int DEC_BLOCKS_PER_SM = (int)((227 * 1024) / (DEC_SMEM + 1024)) < 8 ? (int)((227 * 1024) / (DEC_SMEM + 1024)) : 8;
 }  // namespace
 
@@ -256,9 +263,13 @@ constexpr int DEC_BLOCKS_PER_SM = (int)((227 * 1024) / (DEC_SMEM + 1024)) < 8 ? 
 //  * inv_freq != null: the row of the fused projection is still unrotated; the kernel rotates the
 //    group's query heads itself and (store_kv) the block that owns the newest position rotates
 //    the new key, writes it and the new value to their page, and only then loads that tile;
-//  * splits > 1: every block leaves its partial result in scratch and counts itself in; the last
-//    block to arrive for a (request, head group) merges all splits in split order.  No block
-//    waits for another: whoever comes last does the merge.  `counters` must be zero before
+//  * splits > 1, cluster_merge: the splits of a (request, head group) are one thread-block cluster;
+//    every block leaves its partial result in its own shared memory, the cluster meets at its
+//    barrier, and the first block reads the others' results through distributed shared memory and
+//    merges them in split order.  No global scratch, no fence, no atomic.
+//  * splits > 1 otherwise: every block leaves its partial result in scratch and counts itself in;
+//    the last block to arrive for a (request, head group) merges all splits in split order.  No
+//    block waits for another: whoever comes last does the merge.  `counters` must be zero before
 //    the launch and is zero again after it.
 // Before the dependency wait the kernel only touches what no kernel of the step writes: the
 // step's metadata (block table, positions) and keys and values of earlier steps.
@@ -268,13 +279,14 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
                    const int* __restrict__ meta, int group, const int* __restrict__ cu_tokens,
                    const int* __restrict__ positions, bf16* __restrict__ out, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int* __restrict__ counters, const float* __restrict__ inv_freq, int rot,
-                   int store_kv, int nq, int window, float scale_log2, int num_pages, int splits,
+                   int store_kv, int nq, int window, float scale_log2, int num_pages, int splits, int cluster_merge,
                    int* __restrict__ status) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     // tiles start on 1024-byte boundaries: TMA writes them with the 128-byte swizzle, whose pattern follows the address
     unsigned char* smem_al = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     bf16* qtile = reinterpret_cast<bf16*>(smem_al);
     bf16* tiles = qtile + 16 * LDS;
+    float* share = reinterpret_cast<float*>(smem_al + DEC_MAIN_BYTES);
     __shared__ int s_last;
     __shared__ __align__(8) uint64_t tile_bar[DEC_WARPS][2];  // a warp's stage is full (TMA path)
     pdl_launch_dependents();
@@ -545,6 +557,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
         const int head = kvh * G + r;
         if (splits == 1) {
             out[((size_t)row0 * nq + head) * D + i] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+        } else if (cluster_merge) {
+            share[r * D + i] = acc;
+            if (i == 0) { share[16 * D + 2 * r] = mx; share[16 * D + 2 * r + 1] = lsum; }
         } else {
             size_t slot = ((size_t)e * nq + head) * splits + split;
             part_o[slot * D + i] = acc;
@@ -552,6 +567,43 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
         }
     }
     if (splits == 1) return;
+    if (cluster_merge) {
+        // Every block of the cluster reaches both barriers (a dead request leaves as a whole cluster, above).
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();  // every split's result is in its block's shared memory
+        if (split == 0) {
+            for (int idx = tid; idx < G * D; idx += DEC_WARPS * 32) {
+                int r = idx / D, i = idx % D;
+                float pm[DEC_MAX_CLUSTER], pl[DEC_MAX_CLUSTER], po[DEC_MAX_CLUSTER];
+#pragma unroll
+                for (int s = 0; s < DEC_MAX_CLUSTER; ++s) {  // independent loads, all in flight together
+                    pm[s] = -INFINITY; pl[s] = 0.f; po[s] = 0.f;
+                    if (s < splits) {
+                        const float* remote = cluster.map_shared_rank(share, s);
+                        pm[s] = remote[16 * D + 2 * r];
+                        pl[s] = remote[16 * D + 2 * r + 1];
+                        po[s] = remote[r * D + i];
+                    }
+                }
+                float mx = -INFINITY;
+#pragma unroll
+                for (int s = 0; s < DEC_MAX_CLUSTER; ++s) mx = fmaxf(mx, pm[s]);
+                float lsum = 0.f, acc = 0.f;
+                if (mx > -INFINITY) {
+#pragma unroll
+                    for (int s = 0; s < DEC_MAX_CLUSTER; ++s)
+                        if (s < splits) {
+                            float f = fast_exp2(pm[s] - mx);
+                            lsum += pl[s] * f;
+                            acc += po[s] * f;
+                        }
+                }
+                out[((size_t)row0 * nq + kvh * G + r) * D + i] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+            }
+        }
+        cluster.sync();  // nobody leaves while its shared memory may still be read
+        return;
+    }
     // count this block in; the last one merges the splits of its (request, head group)
     __threadfence();
     __syncthreads();
@@ -807,6 +859,8 @@ extern "C" void attn_set_decode_tma(int on) { g_decode_tma = on; }
 extern "C" int attn_head_dim() { return D; }
 // How many decode blocks fit a multiprocessor (by shared memory): the host sizes the splits by it.
 extern "C" int attn_decode_blocks_per_sm() { return DEC_BLOCKS_PER_SM; }
+// The most splits that can merge through a cluster's shared memory (the portable cluster size).
+extern "C" int attn_decode_max_cluster() { return DEC_MAX_CLUSTER; }
 
 // Float32 words of scratch that attn_decode needs for `splits` > 1: partial outputs and (max, sum) pairs.
 extern "C" size_t attn_decode_scratch_floats(int S, int nq, int splits) {
@@ -837,17 +891,20 @@ extern "C" int attn_prefill(const void* q, int q_stride, const void* cache, cons
                               group, cu_tokens, ctx_lens, (bf16*)out, nq, window, scale * LOG2E, num_pages, bt_cap, status);
 }
 
-// `scratch`: attn_decode_scratch_floats(...) floats when splits > 1.  `counters`: S * nkv ints, zero before the
-// first launch (the kernel leaves them zero).  `inv_freq` (rot/2 floats) switches the fused rotation on: q is
+// `cluster_merge` (splits <= attn_decode_max_cluster()): the splits merge through the cluster's shared memory
+// and neither scratch nor counters is touched.  Otherwise `scratch`: attn_decode_scratch_floats(...) floats when
+// splits > 1, and `counters`: S * nkv ints, zero before the first launch (the kernel leaves them zero).  `inv_freq` (rot/2 floats) switches the fused rotation on: q is
 // then the unrotated projection row and, with store_kv, the new key and value are written here too.
 extern "C" int attn_decode(const void* q, int q_stride, const void* cache, const int* meta, int group,
                            const int* cu_tokens, const int* positions, void* out, float* scratch, int* counters,
                            const float* inv_freq, int rot, int store_kv, int S, int nq, int nkv, int page_size,
-                           int num_pages, int window, float scale, int splits, int max_context, int* status,
-                           cudaStream_t stream) {
+                           int num_pages, int window, float scale, int splits, int cluster_merge, int max_context,
+                           int* status, cudaStream_t stream) {
     if (S <= 0) return 0;
     if (nq % nkv || nq / nkv > 16 || splits < 1) return (int)cudaErrorInvalidValue;
-    if (splits > 1 && (!scratch || !counters)) return (int)cudaErrorInvalidValue;
+    if (splits == 1) cluster_merge = 0;
+    if (cluster_merge && splits > DEC_MAX_CLUSTER) return (int)cudaErrorInvalidValue;
+    if (splits > 1 && !cluster_merge && (!scratch || !counters)) return (int)cudaErrorInvalidValue;
     if (inv_freq && (rot % 2 || rot > D || rot <= 0)) return (int)cudaErrorInvalidValue;
     CacheLayout L{nkv, page_size, D};
     float* part_o = scratch;
@@ -884,8 +941,28 @@ extern "C" int attn_decode(const void* q, int q_stride, const void* cache, const
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
         }
     }
-    dim3 grid(splits, nkv, S);
-    return (int)launch_kernel(attn_decode_kernel, grid, DEC_WARPS * 32, smem, stream, map, use_tma, (bf16*)q, q_stride, (bf16*)cache, L, meta,
-                              group, cu_tokens, positions, (bf16*)out, part_o, part_ml, counters, inv_freq, rot, store_kv, nq,
-                              window, scale * LOG2E, num_pages, splits, status);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(splits, nkv, S);
+    cfg.blockDim = dim3(DEC_WARPS * 32, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (cluster_merge) {  // the splits of a (request, head group) are one cluster
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = splits;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (g_use_pdl & 1) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = na;
+    return (int)cudaLaunchKernelEx(&cfg, attn_decode_kernel, map, use_tma, (bf16*)q, q_stride, (bf16*)cache, L, meta, group,
+                                   cu_tokens, positions, (bf16*)out, part_o, part_ml, counters, inv_freq, rot, store_kv, nq,
+                                   window, scale * LOG2E, num_pages, splits, cluster_merge, status);
 }

@@ -72,7 +72,7 @@ extern "C" int attn_decode_noalloc(const void* q, int q_stride, const void* cach
     }
     int rc = attn_decode(q, q_stride, cache, meta, group, cu_tokens, positions, out, g_scratch_ptr[dev],
                          g_counters_ptr[dev], nullptr, 0, 0, S, nq, nkv, page_size, num_pages, window, scale, splits,
-                         max_context, status, stream);
+                         /*cluster_merge=*/0, max_context, status, stream);
     if (rc != 0) {
         snprintf(msg, sizeof msg, "attn_decode_noalloc: launch failed (%s)", cudaGetErrorString((cudaError_t)rc));
         return fail(rc, err, err_cap, msg);

@@ -23,8 +23,15 @@
 
 namespace cg = cooperative_groups;
 
+#ifndef SM_WARPS
 #define SM_WARPS 8        // warps of a block, splitting K
+#endif
+#ifndef SM_UNROLL
 #define SM_UNROLL 4       // 32-wide k blocks in flight per warp
+#endif
+#ifndef SM_BLOCKS
+#define SM_BLOCKS 3       // blocks a multiprocessor should hold (bounds the registers)
+#endif
 #define SM_MAX_ROWS 16    // rows of x (two n-tiles)
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
@@ -40,7 +47,7 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
 }
 
 template <typename TO, int NT, int EPI>  // NT n-tiles of 8 rows of x; EPI 1: silu(gate) * up
-__global__ void __launch_bounds__(SM_WARPS * 32, 3)  // three blocks a multiprocessor: loads in flight
+__global__ void __launch_bounds__(SM_WARPS * 32, SM_BLOCKS)  // blocks a multiprocessor: loads in flight
 linear_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w, TO* __restrict__ y,
                     int M, int N, int K, int ksplits) {
     __shared__ float red[SM_WARPS][16][NT * 8 + 1];

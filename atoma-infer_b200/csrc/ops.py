@@ -60,6 +60,7 @@ class CudaOps:
         self._attn_libs = {}
         self._attn_tc_libs = {}
         self.tc_attention = os.environ.get("ATOMA_INFER_TC_ATTENTION", "1") != "0"  # tcgen05 prefill attention
+        self.decode_cluster = os.environ.get("ATOMA_INFER_DECODE_CLUSTER", "1") != "0"  # split merge inside a cluster
         self._gemm_lib = None
         self.last_tokens = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # by state slot
         self._counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # split arrivals; kernels leave zeros
@@ -192,16 +193,18 @@ class CudaOps:
             lib = self._attention_library(d)
             if ctx.decode_only:
                 splits = self.decode_splits(S, nkv, ctx.max_context, lib.attn_decode_blocks_per_sm())
-                n = lib.attn_decode_scratch_floats(S, nq, splits)
+                # the splits merge inside a thread-block cluster when they fit one, else through scratch
+                cluster = self.decode_cluster and 1 < splits <= lib.attn_decode_max_cluster()
+                n = 0 if cluster else lib.attn_decode_scratch_floats(S, nq, splits)
                 scratch = torch.empty(n, dtype=torch.float32, device=q.device) if n else None
-                if S * nkv > self._counters.numel():
+                if not cluster and S * nkv > self._counters.numel():
                     raise KernelError(f"decode attention: {S} requests x {nkv} heads exceed the split counters")
                 inv_freq, rot, store = rope if rope is not None else (None, 0, False)
                 self._check(lib.attn_decode(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
                                             _p(ctx.positions), _p(out), _p(scratch), _p(self._counters), _p(inv_freq),
                                             rot, int(store), S, nq, nkv, page_size, num_pages,
-                                            window, ctypes.c_float(scale), splits, ctx.max_context, _p(self.status),
-                                            self._stream()),
+                                            window, ctypes.c_float(scale), splits, int(cluster), ctx.max_context,
+                                            _p(self.status), self._stream()),
                             "attn_decode")
             elif self._prefill_tc(d, page_size, nq, nkv) is not None:
                 tc = self._prefill_tc(d, page_size, nq, nkv)

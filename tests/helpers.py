@@ -1,4 +1,4 @@
-"""Shared test material: two tiny configurations that differ in every size and option,
+"""Shared test material: three tiny configurations that differ in every size and option,
 model folders with random weights, trace builders for the replay program, comparison."""
 from __future__ import annotations
 

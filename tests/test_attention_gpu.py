@@ -74,13 +74,37 @@ def test_prefill_with_cached_context_bf16(rts, d, nq, nkv, page):
     assert worst(got, want) < 2e-2  # values are O(1); bfloat16 P and outputs
 
 
+@pytest.mark.parametrize("cluster", [True, False])
 @pytest.mark.parametrize("d,nq,nkv,page,splits", [(64, 32, 8, 16, 1), (64, 32, 8, 16, 5), (128, 8, 2, 16, 3),
                                                   (16, 4, 2, 4, 2), (64, 3, 1, 8, 4), (256, 4, 1, 16, 2),
-                                                  (96, 12, 4, 32, 7)])
-def test_decode_with_splits_bf16(rts, d, nq, nkv, page, splits):
+                                                  (96, 12, 4, 32, 7), (64, 32, 8, 16, 8), (64, 8, 2, 16, 11)])
+def test_decode_with_splits_bf16(rts, d, nq, nkv, page, splits, cluster):
+    """Splits of the key range merged inside a thread-block cluster (up to eight) or through scratch memory
+    (any number; also what runs when the cluster merge is switched off).  Some requests are shorter than
+    the number of splits, so some blocks have no key at all."""
     entries = [(0, 1), (1, 1), (31, 1), (32, 1), (300, 1), (777, 1), (63, 1)]
-    got, want = run_attention(rts["bfloat16"], entries, nq, nkv, d, page, seed=splits, splits=splits)
+    ops = rts["bfloat16"].ops
+    ops.decode_cluster = cluster
+    try:
+        got, want = run_attention(rts["bfloat16"], entries, nq, nkv, d, page, seed=splits, splits=splits)
+    finally:
+        ops.decode_cluster = True
     assert worst(got, want) < 2e-2
+
+
+def test_cluster_and_scratch_merges_agree_bitwise(rts):
+    """Both merges add the splits in split order with the same arithmetic: the same bits."""
+    ops = rts["bfloat16"].ops
+    entries = [(5, 1), (300, 1), (1029, 1)]
+    outs = []
+    for cluster in (True, False):
+        ops.decode_cluster = cluster
+        try:
+            got, _ = run_attention(rts["bfloat16"], entries, 32, 8, 64, 16, seed=3, splits=6)
+        finally:
+            ops.decode_cluster = True
+        outs.append(torch.cat(got))
+    assert torch.equal(outs[0], outs[1])
 
 
 @pytest.mark.parametrize("window", [1, 5, 64, 100])
