@@ -64,6 +64,10 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     return false;
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
 // ---- TMA
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
@@ -290,6 +294,171 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 2) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// The many-row form as a persistent kernel: one block per multiprocessor walks tiles blockIdx.x,
+// blockIdx.x + gridDim.x, ... (row tiles fastest, so the blocks that run together share a few weight
+// tiles through the L2).  Warp 0 copies (the stage ring runs on across tiles), warp 1 issues the MMAs
+// into one of two accumulators in tensor memory, warps 2..5 are the epilogue: they drain one
+// accumulator (each warp its 32 lanes) while the tensor core fills the other, so the store of a
+// tile costs no tensor-core time.
+template <int BN, int STAGES, typename TO, int EPI>
+__global__ void __launch_bounds__(192)
+gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                       const __grid_constant__ CUtensorMap map_b2, TO* __restrict__ c, int rows_a, int rows_b, int K,
+                       int ldc, int* __restrict__ status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr uint32_t TMEM_COLS = 2 * BN;  // two accumulators
+    static_assert(TMEM_COLS == 256 || TMEM_COLS == 512, "two accumulators of 128 or 256 columns");
+    constexpr int OUT_COLS = EPI == 1 ? BN / 2 : BN;  // output columns of a tile
+    unsigned char* tiles = smem;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* acc_full = empty_bar + STAGES;   // [2]: an accumulator is complete
+    uint64_t* acc_empty = acc_full + 2;        // [2]: the epilogue warps have read it
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tiles_a = (rows_a + BM - 1) / BM, tiles_b = (rows_b + OUT_COLS - 1) / OUT_COLS;
+    const int num_tiles = tiles_a * tiles_b, num_kb = (K + BK - 1) / BK;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 4); }  // one arrival per epilogue warp
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- TMA producer
+            int it = 0, armed = 0;  // k blocks over all my tiles; those whose copies were started
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int a0 = (tile % tiles_a) * BM, b0 = (tile / tiles_a) * OUT_COLS;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    int s = it % STAGES;
+                    uint32_t parity = ((it / STAGES) & 1) ^ 1;  // a fresh barrier passes a wait on parity 1
+                    ok = mbar_wait(&empty_bar[s], parity, status, abort_flag);
+                    if (!ok) break;
+                    unsigned char* a_dst = tiles + s * STAGE_BYTES;
+                    unsigned char* b_dst = a_dst + A_BYTES;
+                    mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+                    tma_load_2d(a_dst, &map_a, kb * BK, a0, &full_bar[s]);
+                    if (EPI == 1) {
+                        tma_load_2d(b_dst, &map_b, kb * BK, b0, &full_bar[s]);                // gate rows
+                        tma_load_2d(b_dst + B_BYTES / 2, &map_b2, kb * BK, b0, &full_bar[s]);  // up rows
+                    } else {
+                        tma_load_2d(b_dst, &map_b, kb * BK, b0, &full_bar[s]);
+                    }
+                    armed = it + 1;
+                }
+            }
+            if (*abort_flag) {
+                // gave up: let the copies already in flight land (bounded) before the block goes away
+                for (int j = max(0, armed - STAGES); j < armed; ++j)
+                    for (uint32_t i = 0; i < WAIT_LIMIT && !mbar_try_wait(&full_bar[j % STAGES], (j / STAGES) & 1); ++i) {}
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- MMA issuer
+            constexpr uint32_t idesc = make_idesc(BM, BN);
+            int it = 0, n = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++n) {
+                const int buf = n & 1;
+                ok = mbar_wait(&acc_empty[buf], (((uint32_t)n >> 1) & 1u) ^ 1u, status, abort_flag);  // its last tile is stored
+                if (!ok) break;
+                tc_fence_after();
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    int s = it % STAGES;
+                    ok = mbar_wait(&full_bar[s], (it / STAGES) & 1, status, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    uint32_t a_addr = smem_u32(tiles + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        uint64_t a_desc = make_desc(a_addr + k * UMMA_K * 2), b_desc = make_desc(b_addr + k * UMMA_K * 2);
+                        umma_bf16(tmem_base + buf * BN, a_desc, b_desc, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[s]);  // the stage is free again when these MMAs have read it
+                }
+                if (ok) umma_commit(&acc_full[buf]);  // arrives when every MMA issued so far is complete
+            }
+        }
+    } else {
+        // ---- epilogue: a warp reaches the 32 lanes of its quarter = rows a0 + 32 * quarter + lane of the tile
+        const int quarter = warp & 3;
+        int n = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++n) {
+            const int a0 = (tile % tiles_a) * BM, b0 = (tile / tiles_a) * OUT_COLS;
+            const int buf = n & 1;
+            ok = mbar_wait(&acc_full[buf], ((uint32_t)n >> 1) & 1u, status, abort_flag);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t acc = tmem_base + buf * BN + ((uint32_t)(quarter * 32) << 16);
+            const int ra = a0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c0 = 0; c0 < OUT_COLS; c0 += 16) {
+                float v[16];
+                if (num_kb > 0) {
+                    tmem_ld16(acc + (uint32_t)c0, v);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = 0.f;
+                }
+                if (EPI == 1 && num_kb > 0) {
+                    float u[16];
+                    tmem_ld16(acc + (uint32_t)(BN / 2 + c0), u);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = v[i] / (1.f + __expf(-v[i])) * u[i];
+                }
+                if (ra < rows_a) {
+                    TO* dst = c + (size_t)ra * ldc + b0 + c0;
+                    const int limit = rows_b - (b0 + c0);  // columns left in the matrix
+                    if (limit >= 16 && (((size_t)dst) & 15) == 0) {
+                        if (sizeof(TO) == 2) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                __nv_bfloat162 p = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                                w[i] = *reinterpret_cast<uint32_t*>(&p);
+                            }
+                            reinterpret_cast<uint4*>(dst)[0] = make_uint4(w[0], w[1], w[2], w[3]);
+                            reinterpret_cast<uint4*>(dst)[1] = make_uint4(w[4], w[5], w[6], w[7]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i)
+                                reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (i < limit) dst[i] = from_float<TO>(v[i]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);  // this warp has read its lanes of the accumulator
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
 // ----------------------------------------------------------------------------- host side
 namespace {
 
@@ -359,19 +528,61 @@ int launch(const void* a, const void* b, void* c, int rows_a, int rows_b, int K,
     return (int)cudaLaunchKernelEx(&cfg, kernel, ma, mb, mb2, (TO*)c, rows_a, rows_b, K, ldc, status);
 }
 
+template <int BN, typename TO, int EPI>
+int launch_persistent(const void* a, const void* b, void* c, int rows_a, int rows_b, int K, int ldc, int* status,
+                      cudaStream_t stream) {
+    constexpr int STAGE_BYTES = BM * BK * 2 + BN * BK * 2;
+    constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+    constexpr size_t SMEM = (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+    CUtensorMap ma, mb, mb2;
+    constexpr int BOX_B = EPI == 1 ? BN / 2 : BN;
+    if (!make_map(&ma, a, rows_a, K, BM)) return (int)cudaErrorInvalidValue;
+    if (!make_map(&mb, b, rows_b, K, BOX_B)) return (int)cudaErrorInvalidValue;
+    const void* b2 = EPI == 1 ? (const void*)((const bf16*)b + (size_t)rows_b * K) : b;
+    if (!make_map(&mb2, b2, rows_b, K, BOX_B)) return (int)cudaErrorInvalidValue;
+    auto kernel = gemm_persistent_kernel<BN, STAGES, TO, EPI>;
+    static bool configured = false;
+    static int sms = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM);
+        if (e != cudaSuccess) return (int)e;
+        int dev = 0;
+        if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int tiles = ((rows_a + BM - 1) / BM) * ((rows_b + BOX_B - 1) / BOX_B);
+    kernel<<<tiles < sms ? tiles : sms, 192, SMEM, stream>>>(ma, mb, mb2, (TO*)c, rows_a, rows_b, K, ldc, status);
+    LAUNCH_RETURN();
+}
+
 }  // namespace
 
 // C = A * B^T.  a [rows_a, K], b [rows_b, K] (for epilogue 1: [2 * rows_b, K], gate rows then up rows),
 // bfloat16, K % 8 == 0, 16-byte aligned.  transpose = 0: c[rows_a, ldc] gets row ra, column rb;
 // transpose = 1: c[rows_b, ldc] gets row rb, column ra.  bn: columns of B per tile (32, 64, 128 or 256).
 // ksplit: blocks (of one cluster) that share a tile's K range, 1..8.
+// persistent (transpose = 0, ksplit = 1 only): one block per multiprocessor walks the tiles and stores a tile while the next is computed.
 extern "C" int gemm_tcgen05(const void* a, const void* b, void* c, int rows_a, int rows_b, int K, int ldc, int out_dtype,
-                            int epilogue, int transpose, int bn, int ksplit, int* status, cudaStream_t stream) {
+                            int epilogue, int transpose, int bn, int ksplit, int persistent, int* status, cudaStream_t stream) {
     if (rows_a <= 0 || rows_b <= 0) return 0;
     if (K % 8 || K <= 0) return (int)cudaErrorInvalidValue;
     if (((uintptr_t)a | (uintptr_t)b) & 15) return (int)cudaErrorInvalidValue;
 #define GO(BN, TO, EPI, TR) return launch<BN, TO, EPI, TR>(a, b, c, rows_a, rows_b, K, ldc, ksplit, status, stream)
     const bool f32 = out_dtype == DT_F32;
+    if (!transpose && ksplit == 1 && persistent) {
+#define GOP(BN, TO, EPI) return launch_persistent<BN, TO, EPI>(a, b, c, rows_a, rows_b, K, ldc, status, stream)
+        if (epilogue == 1) {
+            if (f32) return (int)cudaErrorInvalidValue;
+            if (bn == 256) GOP(256, bf16, 1);
+            if (bn == 128) GOP(128, bf16, 1);
+        } else {
+            if (bn == 256) { if (f32) GOP(256, float, 0); else GOP(256, bf16, 0); }
+            if (bn == 128) { if (f32) GOP(128, float, 0); else GOP(128, bf16, 0); }
+        }
+#undef GOP
+        return (int)cudaErrorInvalidValue;
+    }
     if (!transpose) {
         if (epilogue == 1) {
             if (f32) return (int)cudaErrorInvalidValue;

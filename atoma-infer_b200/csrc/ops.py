@@ -61,6 +61,7 @@ class CudaOps:
         self._attn_tc_libs = {}
         self.tc_attention = os.environ.get("ATOMA_INFER_TC_ATTENTION", "1") != "0"  # tcgen05 prefill attention
         self.decode_cluster = os.environ.get("ATOMA_INFER_DECODE_CLUSTER", "1") != "0"  # split merge inside a cluster
+        self.tc_gemm = os.environ.get("ATOMA_INFER_TC_GEMM", "1") != "0"  # gate/up + SwiGLU of long prompts on tcgen05
         self._gemm_lib = None
         self.last_tokens = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # by state slot
         self._counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # split arrivals; kernels leave zeros
@@ -136,6 +137,8 @@ class CudaOps:
             self._check(self.lib.linear_skinny(_p(x), _p(w), _p(y), _code(y), int(silu_mul), _p(meta), int(use_rows),
                                                M, N, K, self._stream()), "linear_skinny")
             return y
+        if silu_mul and out_dtype == x.dtype and self._swiglu_on_tcgen05(M, n_out, K):
+            return self.gemm_tc(x, w, silu_mul=True, bn=256)
         if out_dtype == torch.float32:
             y = torch.mm(x, w.t(), out_dtype=torch.float32)
         else:
@@ -146,21 +149,35 @@ class CudaOps:
             return out
         return y
 
+    def _swiglu_on_tcgen05(self, M: int, n_out: int, K: int) -> bool:
+        """Whether the gate/up product with the SwiGLU epilogue runs on the persistent tcgen05 kernel instead
+        of the library product followed by the activation kernel.  It wins when its 128 x 128 output tiles
+        fill whole rounds of the multiprocessors (measured at hidden 2048, intermediate 8192: 104 against
+        112 us at 2,048 rows, 198 against 213 us at 4,096; a tie at 1,536; slower below and at 3,000)."""
+        if not self.tc_gemm or M < 1536 or K % 8 or n_out % 8:
+            return False
+        tiles = -(-M // 128) * -(-n_out // 128)
+        rounds = -(-tiles // self.num_sms)
+        return tiles >= 0.97 * rounds * self.num_sms
+
     def gemm_tc(self, a, b, *, out_dtype=None, silu_mul: bool = False, transpose: bool = False, bn: int = 256,
-                ksplit: int = 1):
+                ksplit: int = 1, persistent: bool = True, out=None):
         """C = A * B^T on tcgen05/TMEM with TMA-fed tiles (kernels/gemm_tcgen05.cu).  a [RA, K] fills the
         128-row side of the MMA, b [RB, K] the BN-column side.  ``transpose``: the result is [RB, RA]
         (used with a = weights when the activations have few rows).  ``silu_mul``: b is [gate; up]
-        stacked and the result has RB/2 columns.  ``ksplit``: blocks of a cluster that share a tile's K."""
+        stacked and the result has RB/2 columns.  ``ksplit``: blocks of a cluster that share a tile's K.
+        ``persistent`` (untransposed, unsplit): one block per multiprocessor walks the tiles and stores a tile
+        while the tensor core computes the next."""
         if self._gemm_lib is None:
             self._gemm_lib = build.load_library("gemm_tcgen05", GEMM_SOURCES, cuda=True)
         out_dtype = out_dtype or a.dtype
         ra, K = a.shape
         rb = b.shape[0] // 2 if silu_mul else b.shape[0]
         shape = (rb, ra) if transpose else (ra, rb)
-        c = torch.empty(shape, dtype=out_dtype, device=a.device)
+        c = out if out is not None else torch.empty(shape, dtype=out_dtype, device=a.device)
         self._check(self._gemm_lib.gemm_tcgen05(_p(a), _p(b), _p(c), ra, rb, K, shape[1], _code(c), int(silu_mul),
-                                                int(transpose), bn, ksplit, _p(self.status), self._stream()),
+                                                int(transpose), bn, ksplit, int(persistent and not transpose and ksplit == 1),
+                                                _p(self.status), self._stream()),
                     "gemm_tcgen05")
         return c
 

@@ -214,6 +214,13 @@ def test_repetition_penalty_kernel(rts):
     (3072, 40, 2048, dict(bn=64, transpose=True)),        # weights fill the 128-row side, few activation rows
     (1000, 17, 8192, dict(bn=32, transpose=True)),
     (1000, 100, 264, dict(bn=128, transpose=True, out_dtype=torch.float32)),
+    # one block a multiprocessor walking several tiles each (the default); the one-tile-a-block form
+    (2500, 3000, 328, dict(bn=256)),
+    (2500, 3000, 328, dict(bn=128, silu_mul=True)),
+    (2100, 2900, 136, dict(bn=256, silu_mul=True)),
+    (515, 777, 2048, dict(bn=256, persistent=False)),
+    (260, 320, 192, dict(bn=256, silu_mul=True, persistent=False)),
+    (300, 1000, 200, dict(bn=128, ksplit=3)),             # K split over a cluster, partial tiles added through shared memory
 ])
 def test_tcgen05_gemm(rts, ra, rb, K, kw):
     """The TMA + tcgen05 + TMEM GEMM against a float64 product."""
@@ -231,3 +238,26 @@ def test_tcgen05_gemm(rts, ra, rb, K, kw):
     assert c.shape == ref.shape
     tol = 2e-5 if c.dtype == torch.float32 else 1e-2
     assert (c.double().cpu() - ref).abs().max() < tol * max(1.0, float(ref.abs().max()))
+
+
+def test_linear_swiglu_of_a_long_prompt_runs_on_tcgen05(rts):
+    """ops.linear picks the persistent tcgen05 kernel with the SwiGLU epilogue when the tiles fill whole
+    rounds of the multiprocessors; the result matches the float64 formula either way."""
+    rt = rts["bfloat16"]
+    ops = rt.ops
+    M, n_out, K = 2368, 3968, 136
+    rounds = -(-(19 * 31) // ops.num_sms)
+    chosen = 19 * 31 >= 0.97 * rounds * ops.num_sms
+    assert ops._swiglu_on_tcgen05(M, n_out, K) == chosen  # true on a B200 (148 multiprocessors)
+    assert not ops._swiglu_on_tcgen05(512, n_out, K)
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(2 * n_out, K, generator=g) / math.sqrt(K)).bfloat16()
+    meta = torch.zeros(64, dtype=torch.int32, device=rt.device)
+    meta[0] = M
+    y = ops.linear(x.to(rt.device), w.to(rt.device), silu_mul=True, meta=meta)
+    ops.check_status()
+    ref = x.double() @ w.double().T
+    ref = ref[:, :n_out] * torch.sigmoid(ref[:, :n_out]) * ref[:, n_out:]
+    assert y.shape == ref.shape
+    assert (y.double().cpu() - ref).abs().max() < 2e-2 * max(1.0, float(ref.abs().max()))
