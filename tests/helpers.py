@@ -46,6 +46,31 @@ CONFIG_C = {
 }
 TINY = {"A": (CONFIG_A, 4), "B": (CONFIG_B, 8), "C": (CONFIG_C, 16)}  # name -> (config, page size)
 
+
+
+def _cfg(hidden, inter, vocab, layers, nq, nkv, eps, theta, tie, scaling=None, eos=0):
+    c = {"architectures": ["LlamaForCausalLM"], "hidden_size": hidden, "intermediate_size": inter, "vocab_size": vocab,
+         "num_hidden_layers": layers, "num_attention_heads": nq, "num_key_value_heads": nkv, "rms_norm_eps": eps,
+         "rope_theta": theta, "max_position_embeddings": 2048, "tie_word_embeddings": tie, "eos_token_id": eos}
+    if scaling:
+        c["rope_scaling"] = {"factor": scaling[0], "low_freq_factor": 1.0, "high_freq_factor": scaling[1],
+                             "original_max_position_embeddings": scaling[2], "rope_type": "llama3"}
+    return c
+
+
+# Further geometries, one replay each: other head sizes (32 .. 256 in steps of 16), group sizes 1 .. 16, odd
+# intermediate sizes and vocabularies, an intermediate size below the width, page sizes 4 .. 64.
+# name -> (config, page size)
+MORE = {
+    "d32g2": (_cfg(192, 301, 511, 1, 6, 3, 1e-3, 1e6, True), 32),
+    "d48g1": (_cfg(240, 336, 99, 2, 5, 5, 1e-5, 10000.0, False, scaling=(4.0, 2.0, 32)), 4),
+    "d80g4": (_cfg(640, 1000, 1201, 1, 8, 2, 1e-5, 500000.0, True, scaling=(32.0, 4.0, 64)), 16),
+    "d96g5": (_cfg(960, 520, 300, 2, 10, 2, 1e-6, 500000.0, False), 8),
+    "d256g2": (_cfg(512, 777, 1000, 1, 2, 1, 1e-5, 10000.0, False), 64),
+    "d112g8": (_cfg(896, 1024, 333, 1, 8, 1, 1e-5, 500000.0, True, scaling=(8.0, 4.0, 128)), 16),
+    "d16g16": (_cfg(256, 384, 128, 2, 16, 1, 1e-5, 10000.0, False), 16),
+}
+
 FP32_TOL = 2e-5   # times the largest |logit| of the sequence
 BF16_TOL = 3e-2
 

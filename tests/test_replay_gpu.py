@@ -71,3 +71,23 @@ def test_first_tokens_of_sequences(name, dtype, tiny_models, tmp_path):
     steps, out = helpers.run_trace(d, dtype, steps, str(tmp_path), 256, page)
     worst, where, agree = helpers.compare_trace(steps, out, cfg["vocab_size"], ref)
     assert worst <= (helpers.FP32_TOL if dtype == "float32" else helpers.BF16_TOL), (worst, where)
+
+
+@pytest.mark.parametrize("name", sorted(helpers.MORE))
+def test_other_geometries(name, tmp_path):
+    """One replay (whole, tail decoded one by one, mixed) per further geometry, in both precisions."""
+    cfg, page = helpers.MORE[name]
+    d = helpers.make_model(str(tmp_path / "model"), cfg, seed=len(name))
+    seqs = helpers.random_tokens(cfg["vocab_size"], (2, 37, 90, 150), seed=5)
+    w = helpers.read_weights(d)
+    ref = {k: P.forward(w, cfg, v) for k, v in seqs.items()}
+    families = {"w": helpers.trace_whole(seqs, tag="w"), "t": helpers.trace_tail(seqs, tag="t"),
+                "m": helpers.trace_mixed(seqs, tag="m")}
+    steps = [s for f in families.values() for s in f]
+    max_tokens = sum(-(-len(v) // max(64, page)) * max(64, page) for v in seqs.values())
+    for dtype, tol in (("float32", helpers.FP32_TOL), ("bfloat16", helpers.BF16_TOL)):
+        numbered, out = helpers.run_trace(d, dtype, steps, str(tmp_path / dtype), max_tokens, page)
+        for tag in families:
+            sub = [s for s in numbered if s["entries"][0]["id"].startswith(tag)]
+            worst, where, agree = helpers.compare_trace(sub, out, cfg["vocab_size"], ref)
+            assert worst <= tol, f"{dtype}, family {tag!r}: error {worst:.3g} of the logit scale at {where}"
