@@ -412,9 +412,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
                 if (i < half) {
                     float sn, cs;
                     sincosf((float)pos * inv_freq[i], &sn, &cs);
-                    float xa = __bfloat162float(x[i]), xb = __bfloat162float(x[i + half]);
-                    a = xa * cs - xb * sn;
-                    b = xa * sn + xb * cs;
+                    rotate_pair(__bfloat162float(x[i]), __bfloat162float(x[i + half]), cs, sn, a, b);
                     qtile[toff(r, i)] = __float2bfloat16_rn(a);
                     qtile[toff(r, i + half)] = __float2bfloat16_rn(b);
                 } else {
@@ -439,9 +437,10 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
                 for (int i = tid; i < half; i += DEC_WARPS * 32) {
                     float sn, cs;
                     sincosf((float)pos * inv_freq[i], &sn, &cs);
-                    float xa = __bfloat162float(kx[i]), xb = __bfloat162float(kx[i + half]);
-                    kd[i] = __float2bfloat16_rn(xa * cs - xb * sn);
-                    kd[i + half] = __float2bfloat16_rn(xa * sn + xb * cs);
+                    float lo, hi;
+                    rotate_pair(__bfloat162float(kx[i]), __bfloat162float(kx[i + half]), cs, sn, lo, hi);
+                    kd[i] = __float2bfloat16_rn(lo);
+                    kd[i + half] = __float2bfloat16_rn(hi);
                 }
                 for (int i = rot + tid; i < D; i += DEC_WARPS * 32) kd[i] = kx[i];
                 for (int i = tid; i < D; i += DEC_WARPS * 32) vd[i] = vx[i];

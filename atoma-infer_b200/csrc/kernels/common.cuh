@@ -29,6 +29,32 @@ __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162f
 template <typename T> __device__ __forceinline__ T from_float(float v);
 template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+// Four consecutive elements at once (the address must be a multiple of four elements).
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+    float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+    uint2 t = *reinterpret_cast<const uint2*>(p);
+    float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&t.x)), b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&t.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 t;
+    t.x = *reinterpret_cast<uint32_t*>(&a);
+    t.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = t;
+}
+// The rotation of one pair by an angle whose cosine and sine are given: every product and sum rounded on
+// its own (no fused multiply-add), so that every kernel that rotates gives the same bits.
+__device__ __forceinline__ void rotate_pair(float a, float b, float cs, float sn, float& lo, float& hi) {
+    lo = __fsub_rn(__fmul_rn(a, cs), __fmul_rn(b, sn));
+    hi = __fadd_rn(__fmul_rn(a, sn), __fmul_rn(b, cs));
+}
 
 // Paged cache of one layer: [num_pages, 2 (K, V), num_kv_heads, page_size, head_dim].
 // The (page, K|V, head) block of page_size*head_dim elements is contiguous.

@@ -53,11 +53,13 @@ extern "C" int embed_rows(const int* tokens, const void* table, int table_dtype,
 template <typename TD, typename TO>
 __global__ void __launch_bounds__(256)
 add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, const int* __restrict__ rows,
-                   const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ meta, int H) {
+                   const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ meta, int H,
+                   int aligned) {
     __shared__ float red[33];
     pdl_launch_dependents();
     constexpr int MAXV = 4;  // up to 4 x 4 values per thread stay in registers (H <= 16 * blockDim)
-    const bool in_regs = (H % 4 == 0) && H <= 4 * MAXV * (int)blockDim.x;
+    // four values per access: rows start on multiples of four elements and the buffers on 16 bytes
+    const bool in_regs = aligned && (H % 4 == 0) && H <= 4 * MAXV * (int)blockDim.x;
     float4 wv[MAXV];
     if (in_regs) {  // the norm weight depends on no earlier kernel: fetched before the wait
 #pragma unroll
@@ -83,8 +85,9 @@ add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, cons
             if (i < H) {
                 v[j] = *reinterpret_cast<const float4*>(x + i);
                 if (dl) {
-                    v[j].x += to_float(dl[i]); v[j].y += to_float(dl[i + 1]);
-                    v[j].z += to_float(dl[i + 2]); v[j].w += to_float(dl[i + 3]);
+                    float dv[4];
+                    load4(dl + i, dv);
+                    v[j].x += dv[0]; v[j].y += dv[1]; v[j].z += dv[2]; v[j].w += dv[3];
                     if (!rows) *reinterpret_cast<float4*>(x + i) = v[j];
                 }
                 ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
@@ -97,8 +100,8 @@ add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, cons
         for (int j = 0; j < MAXV; ++j) {
             int i = (threadIdx.x + j * blockDim.x) * 4;
             if (i < H) {
-                o[i] = from_float<TO>(v[j].x * inv * wv[j].x); o[i + 1] = from_float<TO>(v[j].y * inv * wv[j].y);
-                o[i + 2] = from_float<TO>(v[j].z * inv * wv[j].z); o[i + 3] = from_float<TO>(v[j].w * inv * wv[j].w);
+                const float ov[4] = {v[j].x * inv * wv[j].x, v[j].y * inv * wv[j].y, v[j].z * inv * wv[j].z, v[j].w * inv * wv[j].w};
+                store4(o + i, ov);
             }
         }
         return;
@@ -125,9 +128,10 @@ extern "C" int add_rmsnorm(float* resid, const void* delta, int delta_dtype, con
                            cudaStream_t stream) {
     if (n <= 0) return 0;
     int threads = H >= 1024 ? 256 : 128;
+    const int aligned = (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)out | (uintptr_t)w) & 15) == 0;
 #define NORM_CASE(TD, TO) \
     return (int)launch_kernel(add_rmsnorm_kernel<TD, TO>, n, threads, 0, stream, resid, (const TD*)delta, rows, w, eps, \
-                              (TO*)out, meta, H)
+                              (TO*)out, meta, H, aligned)
     if (delta_dtype == DT_F32 && out_dtype == DT_F32) NORM_CASE(float, float);
     else if (delta_dtype == DT_BF16 && out_dtype == DT_BF16) NORM_CASE(__nv_bfloat16, __nv_bfloat16);
     else if (delta_dtype == DT_F32 && out_dtype == DT_BF16) NORM_CASE(float, __nv_bfloat16);
@@ -230,9 +234,10 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int* __restrict_
             float f = i == (int)threadIdx.x ? freq : inv_freq[i];
             float sn, cs;
             sincosf((float)pos * f, &sn, &cs);
-            float a = to_float(x[i]), b = to_float(x[i + half]);
-            dst[i] = from_float<T>(a * cs - b * sn);
-            dst[i + half] = from_float<T>(a * sn + b * cs);
+            float lo, hi;
+            rotate_pair(to_float(x[i]), to_float(x[i + half]), cs, sn, lo, hi);
+            dst[i] = from_float<T>(lo);
+            dst[i + half] = from_float<T>(hi);
         }
         if (is_k)
             for (int i = rot + threadIdx.x; i < d; i += blockDim.x) dst[i] = x[i];  // dims beyond the rotated part
@@ -241,12 +246,95 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int* __restrict_
     }
 }
 
+// The same for many tokens: one block per token.  The token's cosines and sines are computed once (not once
+// per head) and every thread moves 16 bytes at a time: a pair of chunks (the same dims of a head's two
+// halves) for the heads that rotate, single chunks for the values and for dims beyond the rotated part.
+// Needs rot / 2 and the head size to be multiples of a chunk (8 bfloat16 or 4 float32 values).
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_kv_store_rows_kernel(T* __restrict__ qkv, const int* __restrict__ positions, const int* __restrict__ token_entry,
+                          const int* __restrict__ meta, int group, const float* __restrict__ inv_freq,
+                          T* __restrict__ cache, CacheLayout L, int nq, int rot, int store_kv, int num_pages,
+                          int* __restrict__ status) {
+    constexpr int VEC = 16 / sizeof(T);
+    extern __shared__ float trig[];  // cos[half], sin[half]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int d = L.head_dim, nkv = L.num_kv_heads, half = rot / 2;
+    const int t = blockIdx.x;
+    if (t >= meta[META_NUM_TOKENS]) return;
+    const int pos = positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &trig[half + i], &trig[i]);
+    int page = 0;
+    if (store_kv) {
+        const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)token_entry[t] * meta[META_BT_STRIDE + group];
+        page = bt[pos / L.page_size];
+        if (page <= 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicExch(&status[STATUS_BAD_PAGE], 1 + t);
+            page = 0;  // keys and values are dropped; the queries are still rotated
+        }
+    }
+    __syncthreads();
+    T* row = qkv + (size_t)t * (nq + 2 * nkv) * d;
+    const int slot = pos % L.page_size;
+    // items: for each rotating head (q, then k if stored) half/VEC pairs of chunks and (d - rot)/VEC single
+    // chunks (k only: q stays where it is); for each value head d/VEC single chunks
+    const int rot_heads = nq + (page > 0 ? nkv : 0);
+    const int pairs = half / VEC, tail = (d - rot) / VEC, per_rot = pairs + tail;
+    const int items = rot_heads * per_rot + (page > 0 ? nkv * (d / VEC) : 0);
+    for (int it = threadIdx.x; it < items; it += blockDim.x) {
+        if (it < rot_heads * per_rot) {
+            const int h = it / per_rot, j = it % per_rot;
+            const bool is_q = h < nq;
+            const T* x = row + (size_t)h * d;
+            T* dst = is_q ? row + (size_t)h * d : cache + L.offset(page, 0, h - nq, slot);
+            if (j < pairs) {
+                float a[VEC], b[VEC], lo[VEC], hi[VEC];
+#pragma unroll
+                for (int c = 0; c < VEC; c += 4) {
+                    float ta[4], tb[4];
+                    load4(x + j * VEC + c, ta);
+                    load4(x + half + j * VEC + c, tb);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { a[c + i] = ta[i]; b[c + i] = tb[i]; }
+                }
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) rotate_pair(a[i], b[i], trig[j * VEC + i], trig[half + j * VEC + i], lo[i], hi[i]);
+#pragma unroll
+                for (int c = 0; c < VEC; c += 4) {
+                    const float tl[4] = {lo[c], lo[c + 1], lo[c + 2], lo[c + 3]}, th[4] = {hi[c], hi[c + 1], hi[c + 2], hi[c + 3]};
+                    store4(dst + j * VEC + c, tl);
+                    store4(dst + half + j * VEC + c, th);
+                }
+            } else if (!is_q) {  // dims beyond the rotated part travel unchanged
+                const int off = rot + (j - pairs) * VEC;
+                *reinterpret_cast<uint4*>(dst + off) = *reinterpret_cast<const uint4*>(x + off);
+            }
+        } else {
+            const int iv = it - rot_heads * per_rot, h = iv / (d / VEC), j = iv % (d / VEC);
+            const T* x = row + (size_t)(nq + nkv + h) * d + j * VEC;
+            *reinterpret_cast<uint4*>(cache + L.offset(page, 1, h, slot) + j * VEC) = *reinterpret_cast<const uint4*>(x);
+        }
+    }
+}
+
 extern "C" int rope_kv_store(void* qkv, int dtype, const int* positions, const int* token_entry, const int* meta,
                              int group, const float* inv_freq, void* cache, int num_pages, int T, int nq, int nkv,
                              int d, int rot, int page_size, int store_kv, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
     CacheLayout L{nkv, page_size, d};
-    // few tokens: one head per block (many small blocks, short latency); many tokens: eight heads per block
+    // many tokens: one block per token with 16-byte accesses, where the sizes and addresses allow it
+    const int vec = dtype == DT_F32 ? 4 : 8;
+    if (T >= 64 && rot % (2 * vec) == 0 && d % vec == 0 && rot <= 512 && (((uintptr_t)qkv | (uintptr_t)cache) & 15) == 0) {
+        const size_t smem = (size_t)rot * sizeof(float);
+        if (dtype == DT_F32)
+            return (int)launch_kernel(rope_kv_store_rows_kernel<float>, T, 256, smem, stream, (float*)qkv, positions, token_entry,
+                                      meta, group, inv_freq, (float*)cache, L, nq, rot, store_kv, num_pages, status);
+        return (int)launch_kernel(rope_kv_store_rows_kernel<__nv_bfloat16>, T, 256, smem, stream, (__nv_bfloat16*)qkv, positions,
+                                  token_entry, meta, group, inv_freq, (__nv_bfloat16*)cache, L, nq, rot, store_kv,
+                                  num_pages, status);
+    }
+    // few tokens: one head per block (many small blocks, short latency); else eight heads per block
     int heads = nq + 2 * nkv, hpb = T >= 64 ? 8 : 1;
     dim3 threads(d >= 128 ? 64 : 32, hpb);
     dim3 grid(T, (heads + hpb - 1) / hpb);

@@ -118,10 +118,11 @@ def test_swiglu_gate_epilogue(rts, dtype, M):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("many", [False, True])  # few tokens: a block per head; many: a block per token, 16-byte accesses
 @pytest.mark.parametrize("nq,nkv,d,rot,page", [(4, 2, 16, 16, 4), (3, 1, 64, 64, 8), (5, 5, 48, 32, 16)])
-def test_rotation_and_cache_write(rts, dtype, nq, nkv, d, rot, page):
+def test_rotation_and_cache_write(rts, dtype, nq, nkv, d, rot, page, many):
     rt = rts[dtype]
-    entries = [(0, 9), (21, 5), (1000, 1)]  # a long position checks the float32 angle
+    entries = [(0, 40), (21, 30), (1000, 1)] if many else [(0, 9), (21, 5), (1000, 1)]  # a long position checks the float32 angle
     lengths = [c + n for c, n in entries]
     tables, num_pages = K.scrambled_tables(lengths, page)
     ctx, _ = K.make_context(rt, entries, page, tables)
@@ -152,6 +153,20 @@ def test_rotation_and_cache_write(rts, dtype, nq, nkv, d, rot, page):
             row += 1
     untouched = torch.isnan(cache[:, 0, 0, :, 0].float().cpu())
     assert torch.equal(untouched, ~written)  # nothing else was written
+    if many and dtype == "float32":
+        # the same tokens, one request at a time (fewer than 64 tokens a call: the other kernel): the same bits
+        row = 0
+        for (c, n), table in zip(entries, tables):
+            ctx1, _ = K.make_context(rt, [(c, n)], page, [table])
+            part = qkv0[row:row + n].clone().to(rt.device)
+            cache1 = torch.zeros_like(cache)
+            rt.ops.rope_kv_store(part, ctx1.positions, ctx1.token_entry, ctx1.meta, 0, inv.to(rt.device), cache1, num_pages,
+                                 n, nq, nkv, d, rot, page, True)
+            assert torch.equal(part[:, :nq * d], qkv[row:row + n, :nq * d])
+            for i in range(n):
+                pg, slot = table[(c + i) // page], (c + i) % page
+                assert torch.equal(cache1[pg, :, :, slot], cache[pg, :, :, slot])
+            row += n
 
 
 def test_sampling_kernel_against_the_plain_sampler(rts):
