@@ -123,12 +123,65 @@ add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, cons
     }
 }
 
+// The same for many rows of bfloat16 activations: one warp per row, the row's values in registers (NV float4
+// per lane), no block barrier; every lane has all its loads in flight at once.  The sum of squares is taken
+// in another order than above, which bfloat16 results do not show (float32 rows always take the kernel
+// above, whose order never changes).
+template <int NV>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_rows_kernel(float* __restrict__ resid, const __nv_bfloat16* __restrict__ delta, const float* __restrict__ w,
+                        float eps, __nv_bfloat16* __restrict__ out, const int* __restrict__ meta) {
+    constexpr int H = NV * 128;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= meta[META_NUM_TOKENS]) return;
+    float* x = resid + (size_t)r * H;
+    const __nv_bfloat16* dl = delta ? delta + (size_t)r * H : nullptr;
+    float4 v[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) v[j] = *reinterpret_cast<const float4*>(x + (j * 32 + lane) * 4);
+    float ss = 0.f;
+    if (dl) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            float dv[4];
+            load4(dl + (j * 32 + lane) * 4, dv);
+            v[j].x += dv[0]; v[j].y += dv[1]; v[j].z += dv[2]; v[j].w += dv[3];
+            *reinterpret_cast<float4*>(x + (j * 32 + lane) * 4) = v[j];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        ss = fmaf(v[j].x, v[j].x, ss); ss = fmaf(v[j].y, v[j].y, ss);
+        ss = fmaf(v[j].z, v[j].z, ss); ss = fmaf(v[j].w, v[j].w, ss);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float inv = rsqrtf(ss / (float)H + eps);
+    __nv_bfloat16* o = out + (size_t)r * H;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+        const float4 wv = *reinterpret_cast<const float4*>(w + (j * 32 + lane) * 4);
+        const float ov[4] = {v[j].x * inv * wv.x, v[j].y * inv * wv.y, v[j].z * inv * wv.z, v[j].w * inv * wv.w};
+        store4(o + (j * 32 + lane) * 4, ov);
+    }
+}
+
 extern "C" int add_rmsnorm(float* resid, const void* delta, int delta_dtype, const int* rows, const float* w,
                            float eps, void* out, int out_dtype, const int* meta, int n, int H,
                            cudaStream_t stream) {
     if (n <= 0) return 0;
     int threads = H >= 1024 ? 256 : 128;
     const int aligned = (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)out | (uintptr_t)w) & 15) == 0;
+    if (n >= 64 && !rows && aligned && out_dtype == DT_BF16 && (!delta || delta_dtype == DT_BF16) && H % 128 == 0 && H <= 4096) {
+#define ROWS_CASE(NV) \
+    if (H == NV * 128) \
+        return (int)launch_kernel(add_rmsnorm_rows_kernel<NV>, (n + 7) / 8, 256, 0, stream, resid, (const __nv_bfloat16*)delta, w, \
+                                  eps, (__nv_bfloat16*)out, meta)
+        ROWS_CASE(8); ROWS_CASE(16); ROWS_CASE(24); ROWS_CASE(32);
+#undef ROWS_CASE
+    }
 #define NORM_CASE(TD, TO) \
     return (int)launch_kernel(add_rmsnorm_kernel<TD, TO>, n, threads, 0, stream, resid, (const TD*)delta, rows, w, eps, \
                               (TO*)out, meta, H, aligned)

@@ -43,6 +43,30 @@ def test_embedding_and_bad_token_flag(rts, dtype):
         rt.ops.check_status()
 
 
+@pytest.mark.parametrize("H", [1024, 2048, 3072, 4096, 1152, 8192])
+def test_add_rmsnorm_many_rows(rts, H):
+    """64 rows and more of bfloat16 activations take the warp-per-row kernel (widths 1024..4096 in steps of
+    1024); 1152 and 8192 do not fit it and take the block-per-row kernel."""
+    rt = rts["bfloat16"]
+    T, eps = 150, 1e-6
+    g = torch.Generator().manual_seed(H)
+    resid0 = torch.randn(T, H, generator=g) * 3
+    delta = torch.randn(T, H, generator=g).bfloat16()
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    ctx, _ = ctx_for(rt, T)
+    resid = resid0.clone().to(rt.device)
+    out = torch.full((T, H), float("nan"), dtype=torch.bfloat16, device=rt.device)
+    rt.ops.add_rmsnorm(resid, None, w.to(rt.device), eps, out, ctx.meta, T)
+    want = P.rms_norm(resid0.double(), w.double(), eps)
+    assert (out.double().cpu() - want).abs().max() < 2e-2 * want.abs().max()
+    assert torch.equal(resid.cpu(), resid0)
+    rt.ops.add_rmsnorm(resid, delta.to(rt.device), w.to(rt.device), eps, out, ctx.meta, T)
+    summed = resid0 + delta.float()
+    assert torch.equal(resid.cpu(), summed)
+    want = P.rms_norm(summed.double(), w.double(), eps)
+    assert (out.double().cpu() - want).abs().max() < 2e-2 * want.abs().max()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("H", [200, 2048, 3000])
 def test_add_rmsnorm(rts, dtype, H):
