@@ -123,7 +123,7 @@ add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, cons
     }
 }
 
-// The same for many rows of bfloat16 activations: one warp per row, the row's values in registers (NV float4
+// The same for a thousand rows and more of bfloat16 activations (fewer would leave multiprocessors idle): one warp per row, the row's values in registers (NV float4
 // per lane), no block barrier; every lane has all its loads in flight at once.  The sum of squares is taken
 // in another order than above, which bfloat16 results do not show (float32 rows always take the kernel
 // above, whose order never changes).
@@ -174,7 +174,7 @@ extern "C" int add_rmsnorm(float* resid, const void* delta, int delta_dtype, con
     if (n <= 0) return 0;
     int threads = H >= 1024 ? 256 : 128;
     const int aligned = (((uintptr_t)resid | (uintptr_t)delta | (uintptr_t)out | (uintptr_t)w) & 15) == 0;
-    if (n >= 64 && !rows && aligned && out_dtype == DT_BF16 && (!delta || delta_dtype == DT_BF16) && H % 128 == 0 && H <= 4096) {
+    if (n >= 1024 && !rows && aligned && out_dtype == DT_BF16 && (!delta || delta_dtype == DT_BF16) && H % 128 == 0 && H <= 4096) {
 #define ROWS_CASE(NV) \
     if (H == NV * 128) \
         return (int)launch_kernel(add_rmsnorm_rows_kernel<NV>, (n + 7) / 8, 256, 0, stream, resid, (const __nv_bfloat16*)delta, w, \
@@ -376,9 +376,9 @@ extern "C" int rope_kv_store(void* qkv, int dtype, const int* positions, const i
                              int d, int rot, int page_size, int store_kv, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
     CacheLayout L{nkv, page_size, d};
-    // many tokens: one block per token with 16-byte accesses, where the sizes and addresses allow it
+    // hundreds of tokens: one block per token with 16-byte accesses, where the sizes and addresses allow it
     const int vec = dtype == DT_F32 ? 4 : 8;
-    if (T >= 64 && rot % (2 * vec) == 0 && d % vec == 0 && rot <= 512 && (((uintptr_t)qkv | (uintptr_t)cache) & 15) == 0) {
+    if (T >= 256 && rot % (2 * vec) == 0 && d % vec == 0 && rot <= 512 && (((uintptr_t)qkv | (uintptr_t)cache) & 15) == 0) {
         const size_t smem = (size_t)rot * sizeof(float);
         if (dtype == DT_F32)
             return (int)launch_kernel(rope_kv_store_rows_kernel<float>, T, 256, smem, stream, (float*)qkv, positions, token_entry,
