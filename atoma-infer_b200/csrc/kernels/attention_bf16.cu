@@ -649,6 +649,327 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
     }
 }
 
+// ----------------------------------------------------------------------------- decode, large batches
+// The same attention for batches with more (request, head group) pairs than about half the blocks the GPU
+// holds: there, one block per pair (or per fixed split of a pair) leaves a last partial wave of blocks that
+// run almost alone.  Here the grid is as many blocks as the GPU holds at once and the 32-key tiles of all
+// pairs, in (request, head group, key) order, are dealt out evenly: a block takes a contiguous run of
+// tiles, which may end one pair and begin the next (a run is cut into segments at pair boundaries).  A
+// pair that one block covers alone is written directly; otherwise every segment's partial result goes to
+// scratch slot (block index + pair index), a pair's slots being consecutive, and the last block to arrive
+// for the pair merges its slots in order.  No block waits for another.
+namespace {
+constexpr size_t FLAT_SMEM_FIXED = DEC_MAIN_BYTES;  // then (requests + 1) ints: tiles before each request
+}
+
+__global__ void __launch_bounds__(DEC_WARPS * 32)
+attn_decode_flat_kernel(bf16* __restrict__ q, int q_stride, bf16* __restrict__ cache, CacheLayout L,
+                        const int* __restrict__ meta, int group, const int* __restrict__ cu_tokens,
+                        const int* __restrict__ positions, bf16* __restrict__ out, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, int* __restrict__ counters, const float* __restrict__ inv_freq, int rot,
+                        int store_kv, int nq, int window, float scale_log2, int num_pages, int S,
+                        int* __restrict__ status) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* qtile = reinterpret_cast<bf16*>(smem_raw);
+    bf16* tiles = qtile + 16 * LDS;
+    int* prefix = reinterpret_cast<int*>(smem_raw + FLAT_SMEM_FIXED);  // [S + 1]
+    __shared__ int s_last;
+    pdl_launch_dependents();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nkv = L.num_kv_heads, G = nq / nkv;
+    // tiles of every request (one head group's worth), then their running sum; only the step's metadata is read
+    const int live = min(S, meta[META_NUM_ENTRIES]);
+    for (int e = tid; e < S; e += DEC_WARPS * 32) {
+        int n = 0;
+        if (e < live) {
+            const int kv_len = positions[cu_tokens[e]] + 1;
+            const int ks = window > 0 ? max(0, kv_len - window) : 0;
+            n = (kv_len - ks + DEC_KT - 1) / DEC_KT;
+        }
+        prefix[e + 1] = n;
+    }
+    if (tid == 0) prefix[0] = 0;
+    __syncthreads();
+    if (warp == 0) {
+        int carry = 0;
+        for (int base = 1; base <= S; base += 32) {
+            const int i = base + lane;
+            int v = i <= S ? prefix[i] : 0;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                int u = __shfl_up_sync(0xffffffffu, v, off);
+                if (lane >= off) v += u;
+            }
+            if (i <= S) prefix[i] = v + carry;
+            carry += __shfl_sync(0xffffffffu, v, 31);
+        }
+    }
+    __syncthreads();
+    const int total = prefix[S] * nkv;
+    const int per = (total + (int)gridDim.x - 1) / (int)gridDim.x;  // tiles per block
+    int t = blockIdx.x * per;
+    const int t_end = min(total, t + per);
+    pdl_wait();  // q (and, without the fused rotation, the newest key and value) come from the kernels before
+    if (t >= t_end) return;
+    int e = 0;
+    {   // the request that holds tile t: the last one whose first tile is not beyond it
+        int lo_e = 0, hi_e = S - 1;
+        while (lo_e < hi_e) {
+            int mid = (lo_e + hi_e + 1) >> 1;
+            if (prefix[mid] * nkv <= t) lo_e = mid; else hi_e = mid - 1;
+        }
+        e = lo_e;
+    }
+    constexpr int PAIRS = D / 16, RPL = DEC_KT * PAIRS / 32;  // 32-byte sectors per row; rows*sectors per lane
+    const int ps = L.page_size;
+    const int ps_shift = (ps & (ps - 1)) == 0 ? 31 - __clz(ps) : -1;
+    const size_t v_off = (size_t)nkv * ps * D, page_stride = 2 * v_off;
+    bf16* mine = tiles + warp * DEC_WARP_ELEMS;
+    const int g = lane >> 2, tig = lane & 3;
+
+    while (t < t_end) {
+        while (prefix[e + 1] * nkv <= t) ++e;  // requests without tiles are stepped over
+        const int nt_e = prefix[e + 1] - prefix[e];
+        const int rel = t - prefix[e] * nkv;
+        const int kvh = rel / nt_e, tile0 = rel % nt_e;
+        const int tile1 = min(nt_e, tile0 + (t_end - t));
+        const int ntiles = tile1 - tile0;
+        const int pair = e * nkv + kvh, pair_begin = prefix[e] * nkv + kvh * nt_e;
+        const int first_block = pair_begin / per, parts = (pair_begin + nt_e - 1) / per - first_block + 1;
+        const int row0 = cu_tokens[e], kv_len = positions[row0] + 1;
+        const int kstart = window > 0 ? max(0, kv_len - window) : 0;
+        const int lo = kstart + tile0 * DEC_KT, hi = min(kv_len, kstart + tile1 * DEC_KT);
+        const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)e * meta[META_BT_STRIDE + group];
+        const size_t head_off = (size_t)kvh * ps * D;
+        auto fetch_pages = [&](int tt, int (&pg)[RPL]) {
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) {
+                int pos = lo + tt * DEC_KT + (lane + 32 * i) / PAIRS;
+                pg[i] = -1;
+                if (pos < hi) pg[i] = __ldg(bt + (ps_shift >= 0 ? pos >> ps_shift : pos / ps));
+            }
+        };
+        auto load_tile = [&](int tt, int stage, const int (&pg)[RPL]) {
+            bf16* ktile = mine + stage * 2 * DEC_KT * LDS;
+            bf16* vtile = ktile + DEC_KT * LDS;
+#pragma unroll
+            for (int i = 0; i < RPL; ++i) {
+                int idx = lane + 32 * i, r = idx / PAIRS, c = (idx % PAIRS) * 16;
+                int pos = lo + tt * DEC_KT + r;
+                int o0 = toff(r, c), o1 = toff(r, c + 8);
+                int page = pg[i];
+                if (pos < hi && (page <= 0 || page >= num_pages)) {
+                    atomicExch(&status[STATUS_BAD_PAGE], 1 + pos);
+                    page = -1;
+                }
+                if (page > 0) {
+                    int slot = ps_shift >= 0 ? pos & (ps - 1) : pos % ps;
+                    const bf16* src = cache + (size_t)page * page_stride + head_off + (size_t)slot * D + c;
+                    cp_async_16(ktile + o0, src);
+                    cp_async_16(ktile + o1, src + 8);
+                    cp_async_16(vtile + o0, src + v_off);
+                    cp_async_16(vtile + o1, src + v_off + 8);
+                } else {  // beyond the segment: zeros (a value row nobody wrote must not reach P*V)
+                    uint4 z = make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(ktile + o0) = z;
+                    *reinterpret_cast<uint4*>(ktile + o1) = z;
+                    *reinterpret_cast<uint4*>(vtile + o0) = z;
+                    *reinterpret_cast<uint4*>(vtile + o1) = z;
+                }
+            }
+        };
+        int pg_cur[RPL], pg_nxt[RPL];
+        if (warp < ntiles) fetch_pages(warp, pg_cur);
+        if (warp + DEC_WARPS < ntiles) fetch_pages(warp + DEC_WARPS, pg_nxt);
+        // every key but the newest is older than this step: a first tile without it can be fetched at once
+        const bool first_is_old = warp < ntiles && lo + (warp + 1) * DEC_KT <= kv_len - 1;
+        if (first_is_old) load_tile(warp, 0, pg_cur);
+        cp_async_commit();
+
+        // ---- the group's queries into the tile (rotated here when the rotation is fused), the newest key and value
+        if (inv_freq) {
+            const int half = rot / 2, pos = kv_len - 1;
+            const bf16* row = q + (size_t)row0 * q_stride;
+            for (int idx = tid; idx < 16 * (D / 2); idx += DEC_WARPS * 32) {
+                int r = idx / (D / 2), i = idx % (D / 2);
+                if (r < G) {
+                    const bf16* x = row + (size_t)(kvh * G + r) * D;
+                    if (i < half) {
+                        float sn, cs, a, b;
+                        sincosf((float)pos * inv_freq[i], &sn, &cs);
+                        rotate_pair(__bfloat162float(x[i]), __bfloat162float(x[i + half]), cs, sn, a, b);
+                        qtile[toff(r, i)] = __float2bfloat16_rn(a);
+                        qtile[toff(r, i + half)] = __float2bfloat16_rn(b);
+                    } else {  // dims beyond the rotated part, two to a slot
+                        int j = rot + 2 * (i - half);
+                        qtile[toff(r, j)] = x[j];
+                        qtile[toff(r, j + 1)] = x[j + 1];
+                    }
+                } else {
+                    qtile[toff(r, 2 * i)] = __float2bfloat16_rn(0.f);
+                    qtile[toff(r, 2 * i + 1)] = __float2bfloat16_rn(0.f);
+                }
+            }
+            if (store_kv && hi == kv_len) {  // this segment owns the newest position: its key and value go to their page first
+                int page = bt[pos / ps];
+                if (page > 0 && page < num_pages) {
+                    const bf16* kx = row + (size_t)(nq + kvh) * D;
+                    const bf16* vx = row + (size_t)(nq + nkv + kvh) * D;
+                    bf16* kd = cache + L.offset(page, 0, kvh, pos % ps);
+                    bf16* vd = cache + L.offset(page, 1, kvh, pos % ps);
+                    for (int i = tid; i < half; i += DEC_WARPS * 32) {
+                        float sn, cs, a, b;
+                        sincosf((float)pos * inv_freq[i], &sn, &cs);
+                        rotate_pair(__bfloat162float(kx[i]), __bfloat162float(kx[i + half]), cs, sn, a, b);
+                        kd[i] = __float2bfloat16_rn(a);
+                        kd[i + half] = __float2bfloat16_rn(b);
+                    }
+                    for (int i = rot + tid; i < D; i += DEC_WARPS * 32) kd[i] = kx[i];
+                    for (int i = tid; i < D; i += DEC_WARPS * 32) vd[i] = vx[i];
+                    __threadfence();
+                }
+            }
+        } else {
+            for (int idx = tid; idx < 16 * (D / 8); idx += DEC_WARPS * 32) {
+                int r = idx / (D / 8), c = idx % (D / 8);
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (r < G) v = *reinterpret_cast<const uint4*>(q + (size_t)row0 * q_stride + (size_t)(kvh * G + r) * D + c * 8);
+                *reinterpret_cast<uint4*>(qtile + toff(r, c * 8)) = v;
+            }
+        }
+        __syncthreads();
+        if (warp < ntiles && !first_is_old) load_tile(warp, 0, pg_cur);
+        cp_async_commit();
+
+        uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
+        if (Q_IN_REGS) {
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) load_a_frag(qf[ks], qtile, ks, lane);
+        }
+        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        float o[DTILES][4];
+#pragma unroll
+        for (int dt = 0; dt < DTILES; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+        for (int tt = warp, it = 0; tt < ntiles; tt += DEC_WARPS, ++it) {
+            int stage = 0;
+            if (DEC_STAGES == 2) {
+                stage = it & 1;
+                if (tt + DEC_WARPS < ntiles) load_tile(tt + DEC_WARPS, stage ^ 1, pg_nxt);
+                cp_async_commit();
+                if (tt + 2 * DEC_WARPS < ntiles) fetch_pages(tt + 2 * DEC_WARPS, pg_nxt);  // arrives while this tile is computed
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            bf16* ktile = mine + stage * 2 * DEC_KT * LDS;
+            bf16* vtile = ktile + DEC_KT * LDS;
+            __syncwarp();
+            float s[DEC_NK][4];
+            qk_tile<DEC_NK>(s, qf, qtile, ktile, lane);
+            const int k0 = lo + tt * DEC_KT;
+#pragma unroll
+            for (int n = 0; n < DEC_NK; ++n)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    int key = k0 + n * 8 + (lane & 3) * 2 + (c & 1);
+                    s[n][c] = key < hi ? s[n][c] * scale_log2 : -INFINITY;
+                }
+            softmax_tile<DEC_NK>(s, m, l, o);
+            pv_tile<DEC_NK>(o, s, vtile, lane);
+            __syncwarp();
+            if (DEC_STAGES == 1) {
+                if (tt + DEC_WARPS < ntiles) {
+                    load_tile(tt + DEC_WARPS, 0, pg_nxt);
+                    if (tt + 2 * DEC_WARPS < ntiles) fetch_pages(tt + 2 * DEC_WARPS, pg_nxt);
+                }
+                cp_async_commit();
+            }
+        }
+        cp_async_wait<0>();
+        __syncthreads();  // every warp is done with its tiles: the space becomes the merge buffer
+        float* mbuf = reinterpret_cast<float*>(tiles);
+        float* wm = mbuf + warp * (32 + 16 * D);  // m[16], l[16], o[16][D]
+        if (tig == 0) {
+            wm[g] = m[0]; wm[g + 8] = m[1];
+            wm[16 + g] = l[0]; wm[16 + g + 8] = l[1];
+        }
+#pragma unroll
+        for (int dt = 0; dt < DTILES; ++dt) {
+            int dim = dt * 8 + tig * 2;
+            wm[32 + g * D + dim] = o[dt][0]; wm[32 + g * D + dim + 1] = o[dt][1];
+            wm[32 + (g + 8) * D + dim] = o[dt][2]; wm[32 + (g + 8) * D + dim + 1] = o[dt][3];
+        }
+        __syncthreads();
+        const size_t slot = (size_t)blockIdx.x + pair;
+        for (int idx = tid; idx < G * D; idx += DEC_WARPS * 32) {
+            int r = idx / D, i = idx % D;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < DEC_WARPS; ++w) mx = fmaxf(mx, mbuf[w * (32 + 16 * D) + r]);
+            float lsum = 0.f, acc = 0.f;
+            if (mx > -INFINITY) {
+#pragma unroll
+                for (int w = 0; w < DEC_WARPS; ++w) {
+                    const float* p = mbuf + w * (32 + 16 * D);
+                    float f = fast_exp2(p[r] - mx);
+                    lsum += p[16 + r] * f;
+                    acc += p[32 + r * D + i] * f;
+                }
+            }
+            if (parts == 1) {
+                out[((size_t)row0 * nq + kvh * G + r) * D + i] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+            } else {
+                part_o[(slot * G + r) * D + i] = acc;
+                if (i == 0) { part_ml[(slot * G + r) * 2] = mx; part_ml[(slot * G + r) * 2 + 1] = lsum; }
+            }
+        }
+        if (parts > 1) {
+            // count this segment in; the last one merges the pair's slots (first_block + pair ... in order)
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) {
+                int old = atomicAdd(counters + pair, 1);
+                s_last = old == parts - 1;
+                if (s_last) counters[pair] = 0;  // as it was found, for the next launch
+            }
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                const size_t slot0 = (size_t)first_block + pair;
+                for (int idx = tid; idx < G * D; idx += DEC_WARPS * 32) {
+                    int r = idx / D, i = idx % D;
+                    float mx = -INFINITY;
+                    for (int sp = 0; sp < parts; ++sp) mx = fmaxf(mx, __ldcg(part_ml + ((slot0 + sp) * G + r) * 2));
+                    float lsum = 0.f, acc = 0.f;
+                    if (mx > -INFINITY) {
+                        for (int s0 = 0; s0 < parts; s0 += 4) {
+                            float pm[4], pl[4], po[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {  // independent loads, in flight together
+                                const bool on = s0 + j < parts;
+                                const size_t sl = slot0 + (on ? s0 + j : 0);
+                                pm[j] = on ? __ldcg(part_ml + (sl * G + r) * 2) : -INFINITY;
+                                pl[j] = on ? __ldcg(part_ml + (sl * G + r) * 2 + 1) : 0.f;
+                                po[j] = on ? __ldcg(part_o + (sl * G + r) * D + i) : 0.f;
+                            }
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                if (s0 + j < parts) {
+                                    float f = fast_exp2(pm[j] - mx);
+                                    lsum += pl[j] * f;
+                                    acc += po[j] * f;
+                                }
+                        }
+                    }
+                    out[((size_t)row0 * nq + kvh * G + r) * D + i] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+                }
+            }
+        }
+        t += ntiles;
+        __syncthreads();  // the merge buffer and the query tile are free for the next segment
+    }
+}
+
 // ----------------------------------------------------------------------------- prefill (and mixed steps)
 namespace {
 constexpr int PF_KT = 64;                 // keys per tile
@@ -888,6 +1209,56 @@ extern "C" int attn_prefill(const void* q, int q_stride, const void* cache, cons
     }
     return (int)launch_kernel(attn_prefill_kernel, grid, 128, smem, stream, (const bf16*)q, q_stride, (const bf16*)cache, L, meta,
                               group, cu_tokens, ctx_lens, (bf16*)out, nq, window, scale * LOG2E, num_pages, bt_cap, status);
+}
+
+namespace {
+// The flat kernel's dynamic shared memory limit grows only (one place for both callers), and is not set
+// again inside a stream capture once it is large enough.
+cudaError_t flat_allow_smem(size_t smem) {
+    static size_t configured = 0;
+    if (smem <= configured) return cudaSuccess;
+    cudaError_t err = cudaFuncSetAttribute(attn_decode_flat_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err == cudaSuccess) configured = smem;
+    return err;
+}
+}  // namespace
+
+// How many blocks of the flat kernel the current GPU holds at once for S requests (its grid size).
+extern "C" int attn_decode_flat_blocks(int S) {
+    const size_t smem = FLAT_SMEM_FIXED + (size_t)(S + 1) * sizeof(int);
+    int dev = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    if (smem > 227 * 1024 || flat_allow_smem(smem) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_flat_kernel, DEC_WARPS * 32, smem) != cudaSuccess) return 0;
+    return sms * per_sm;
+}
+
+// Floats of scratch for attn_decode_flat: a partial result per (block, pair) slot.
+extern "C" size_t attn_decode_flat_scratch_floats(int S, int nq, int nkv, int blocks) {
+    return (size_t)(blocks + S * nkv) * (nq / nkv) * (D + 2);
+}
+
+// Decode attention for large batches: `blocks` blocks share all key tiles evenly (see the kernel).  `scratch`:
+// attn_decode_flat_scratch_floats(...) floats; `counters`: S * nkv ints, zero before the first launch (left zero).
+extern "C" int attn_decode_flat(const void* q, int q_stride, const void* cache, const int* meta, int group,
+                                const int* cu_tokens, const int* positions, void* out, float* scratch, int* counters,
+                                const float* inv_freq, int rot, int store_kv, int S, int nq, int nkv, int page_size,
+                                int num_pages, int window, float scale, int blocks, int* status, cudaStream_t stream) {
+    if (S <= 0) return 0;
+    if (nq % nkv || nq / nkv > 16 || blocks < 1 || !scratch || !counters) return (int)cudaErrorInvalidValue;
+    if (inv_freq && (rot % 2 || rot > D || rot <= 0)) return (int)cudaErrorInvalidValue;
+    CacheLayout L{nkv, page_size, D};
+    const size_t slots = (size_t)blocks + (size_t)S * nkv;
+    float* part_o = scratch;
+    float* part_ml = scratch + slots * (nq / nkv) * D;
+    const size_t smem = FLAT_SMEM_FIXED + (size_t)(S + 1) * sizeof(int);
+    if (smem > 227 * 1024) return (int)cudaErrorInvalidValue;
+    cudaError_t err = flat_allow_smem(smem);
+    if (err != cudaSuccess) return (int)err;
+    return (int)launch_kernel(attn_decode_flat_kernel, blocks, DEC_WARPS * 32, smem, stream, (bf16*)q, q_stride, (bf16*)cache, L, meta,
+                              group, cu_tokens, positions, (bf16*)out, part_o, part_ml, counters, inv_freq, rot, store_kv, nq,
+                              window, scale * LOG2E, num_pages, S, status);
 }
 
 // `cluster_merge` (splits <= attn_decode_max_cluster()): the splits merge through the cluster's shared memory

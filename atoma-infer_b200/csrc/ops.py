@@ -62,6 +62,12 @@ class CudaOps:
         self.tc_attention = os.environ.get("ATOMA_INFER_TC_ATTENTION", "1") != "0"  # tcgen05 prefill attention
         self.decode_cluster = os.environ.get("ATOMA_INFER_DECODE_CLUSTER", "1") != "0"  # split merge inside a cluster
         self.tc_gemm = os.environ.get("ATOMA_INFER_TC_GEMM", "1") != "0"  # gate/up + SwiGLU of long prompts on tcgen05
+        # large decode batches: key tiles dealt out evenly over as many blocks as the GPU holds ("0": never;
+        # a number above 1: always, with that many blocks, for experiments and tests)
+        flat = os.environ.get("ATOMA_INFER_DECODE_FLAT", "1")
+        self.decode_flat = flat != "0"
+        self.decode_flat_forced = int(flat) if flat.isdigit() and int(flat) > 1 else 0
+        self._flat_blocks = {}
         self._gemm_lib = None
         self.last_tokens = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # by state slot
         self._counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # split arrivals; kernels leave zeros
@@ -209,6 +215,20 @@ class CudaOps:
         if self.fast_attention(q.dtype, d, nq, nkv, q_stride):
             lib = self._attention_library(d)
             if ctx.decode_only:
+                inv_freq, rot, store = rope if rope is not None else (None, 0, False)
+                flat_blocks = self._decode_flat_blocks(lib, d, S, nkv)
+                if flat_blocks:
+                    # large batch: as many blocks as the GPU holds share all key tiles evenly
+                    n = lib.attn_decode_flat_scratch_floats(S, nq, nkv, flat_blocks)
+                    scratch = torch.empty(n, dtype=torch.float32, device=q.device)
+                    if S * nkv > self._counters.numel():
+                        raise KernelError(f"decode attention: {S} requests x {nkv} heads exceed the split counters")
+                    self._check(lib.attn_decode_flat(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group,
+                                                     _p(ctx.cu_tokens), _p(ctx.positions), _p(out), _p(scratch),
+                                                     _p(self._counters), _p(inv_freq), rot, int(store), S, nq, nkv,
+                                                     page_size, num_pages, window, ctypes.c_float(scale), flat_blocks,
+                                                     _p(self.status), self._stream()), "attn_decode_flat")
+                    return
                 splits = self.decode_splits(S, nkv, ctx.max_context, lib.attn_decode_blocks_per_sm())
                 # the splits merge inside a thread-block cluster when they fit one, else through scratch
                 cluster = self.decode_cluster and 1 < splits <= lib.attn_decode_max_cluster()
@@ -216,7 +236,6 @@ class CudaOps:
                 scratch = torch.empty(n, dtype=torch.float32, device=q.device) if n else None
                 if not cluster and S * nkv > self._counters.numel():
                     raise KernelError(f"decode attention: {S} requests x {nkv} heads exceed the split counters")
-                inv_freq, rot, store = rope if rope is not None else (None, 0, False)
                 self._check(lib.attn_decode(_p(q), q_stride, _p(cache_layer), _p(ctx.meta), group, _p(ctx.cu_tokens),
                                             _p(ctx.positions), _p(out), _p(scratch), _p(self._counters), _p(inv_freq),
                                             rot, int(store), S, nq, nkv, page_size, num_pages,
@@ -242,6 +261,20 @@ class CudaOps:
                                           num_pages, window, ctypes.c_float(scale), _p(self.status), self._stream()),
                     "attn_generic")
 
+    def _decode_flat_blocks(self, lib, d: int, S: int, nkv: int) -> int:
+        """Grid size of the flat decode kernel if this batch should take it (at least half as many (request,
+        head group) pairs as blocks the GPU holds: below that, fixed splits in clusters fill the GPU as well
+        and merge faster), else 0."""
+        if not self.decode_flat:
+            return 0
+        if self.decode_flat_forced:
+            return self.decode_flat_forced
+        key = (d, S)
+        blocks = self._flat_blocks.get(key)
+        if blocks is None:
+            blocks = self._flat_blocks[key] = int(lib.attn_decode_flat_blocks(S))
+        return blocks if blocks and 2 * S * nkv >= blocks else 0
+
     def _prefill_tc(self, d: int, page_size: int, nq: int, nkv: int):
         """The tcgen05 prefill attention library for this geometry, or None (then the mma.sync kernel runs)."""
         if d not in ATTENTION_TC_HEAD_DIMS or not self.tc_attention:
@@ -259,6 +292,7 @@ class CudaOps:
         if lib is None:
             lib = build.load_library(f"attention_d{d}", ATTENTION_SOURCES, cuda=True, defines={"HEAD_DIM": d})
             lib.attn_decode_scratch_floats.restype = ctypes.c_size_t
+            lib.attn_decode_flat_scratch_floats.restype = ctypes.c_size_t
             lib.kernels_set_pdl(1 if self.pdl else 0)
             # page loads of the decode kernel by TMA: measured no faster than cp.async (13.1 vs 15.4 us at batch 8), so opt-in
             lib.attn_set_decode_tma(int(os.environ.get("ATOMA_INFER_DECODE_TMA", "0") == "1"))

@@ -161,13 +161,14 @@ def number(steps):
     return [dict(s, step=i) for i, s in enumerate(steps)]
 
 
-def run_trace(model_dir: str, dtype: str, steps, out_dir: str, max_tokens: int, page_size: int, timeout=600):
+def run_trace(model_dir: str, dtype: str, steps, out_dir: str, max_tokens: int, page_size: int, timeout=600, env=None):
     """Runs bin/trace_run as a user would; returns the list of per-step arrays (None where nothing was wanted)."""
     steps = number(steps)
     text = "\n".join(json.dumps(s) for s in steps) + "\n"
     cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
            "--out", out_dir, "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
-    p = subprocess.run(cmd, input=text, capture_output=True, text=True, timeout=timeout)
+    p = subprocess.run(cmd, input=text, capture_output=True, text=True, timeout=timeout,
+                       env=dict(os.environ, **env) if env else None)
     assert p.returncode == 0, f"trace_run failed ({p.returncode}):\n{p.stdout[-2000:]}\n{p.stderr[-4000:]}"
     done = [l for l in p.stdout.splitlines() if l.startswith("done ")]
     assert [int(l.split()[1]) for l in done] == [s["step"] for s in steps], "a 'done <step>' line is missing"

@@ -92,6 +92,25 @@ def test_decode_with_splits_bf16(rts, d, nq, nkv, page, splits, cluster):
     assert worst(got, want) < 2e-2
 
 
+@pytest.mark.parametrize("blocks", [1, 2, 5, 37, 444])
+@pytest.mark.parametrize("d,nq,nkv,page", [(64, 32, 8, 16), (128, 8, 2, 16), (16, 4, 2, 4), (96, 12, 4, 32), (256, 2, 1, 16)])
+def test_decode_flat_bf16(rts, d, nq, nkv, page, blocks):
+    """The large-batch decode kernel: a fixed number of blocks share all key tiles evenly, a block's run of tiles
+    may span several requests and head groups, a pair may be spread over many blocks (or lie inside one)."""
+    entries = [(0, 1), (1, 1), (31, 1), (32, 1), (300, 1), (777, 1), (63, 1), (64, 1), (500, 1)]
+    ops = rts["bfloat16"].ops
+    ops._decode_flat_blocks = lambda *a: blocks
+    try:
+        got, want = run_attention(rts["bfloat16"], entries, nq, nkv, d, page, seed=blocks)
+        assert worst(got, want) < 2e-2
+        got, want = run_attention(rts["bfloat16"], entries, nq, nkv, d, page, seed=blocks, window=100)
+        assert worst(got, want) < 2e-2
+        got, want = run_attention(rts["bfloat16"], [(599, 1), (700, 1)], nq, nkv, d, page, seed=255, stand_out=255, scale=1.0)
+        assert worst(got, want) < 3e-2
+    finally:
+        del ops._decode_flat_blocks
+
+
 def test_cluster_and_scratch_merges_agree_bitwise(rts):
     """Both merges add the splits in split order with the same arithmetic: the same bits."""
     ops = rts["bfloat16"].ops
@@ -152,9 +171,10 @@ def test_head_sizes_beyond_the_kernels_are_refused(rts):
         run_attention(rts["bfloat16"], [(0, 4)], 1, 1, 272, 16)
 
 
+@pytest.mark.parametrize("flat", [0, 3, 100])  # 0: fixed splits; else the large-batch kernel with that many blocks
 @pytest.mark.parametrize("d,rot,nq,nkv,page,splits", [(64, 64, 32, 8, 16, 3), (64, 64, 3, 1, 8, 1), (128, 64, 8, 2, 16, 2),
                                                        (16, 16, 4, 2, 4, 4)])
-def test_decode_with_fused_rotation_and_cache_write(rts, d, rot, nq, nkv, page, splits):
+def test_decode_with_fused_rotation_and_cache_write(rts, d, rot, nq, nkv, page, splits, flat):
     """The decode kernel given unrotated q, k, v of the new token: it must rotate q, write the rotated
     key and the value to the right page and slot, and attend over old keys and the new one."""
     rt = rts["bfloat16"]
@@ -183,11 +203,13 @@ def test_decode_with_fused_rotation_and_cache_write(rts, d, rot, nq, nkv, page, 
         qkv[i] = torch.cat([qs[i][-1].reshape(-1), ks[i][-1].reshape(-1), vs[i][-1].reshape(-1)]).bfloat16()
     out = torch.full((S, nq * d), float("nan"), dtype=torch.bfloat16, device=rt.device)
     rt.ops.decode_splits = lambda *a: splits
+    rt.ops._decode_flat_blocks = lambda *a: flat
     try:
         rt.ops.attention(qkv, qkv.shape[1], cache, ctx, 0, out, nq, nkv, d, page, num_pages, 0, 1 / math.sqrt(d),
                          rope=(inv.to(rt.device), rot, True))
     finally:
         del rt.ops.decode_splits
+        del rt.ops._decode_flat_blocks
     rt.ops.check_status()
     for i, c in enumerate(contexts):
         want = P.causal_attention(rqs[i].double(), rks[i].double(), vs[i].double(), 1 / math.sqrt(d))[-1]

@@ -91,3 +91,32 @@ def test_other_geometries(name, tmp_path):
             sub = [s for s in numbered if s["entries"][0]["id"].startswith(tag)]
             worst, where, agree = helpers.compare_trace(sub, out, cfg["vocab_size"], ref)
             assert worst <= tol, f"{dtype}, family {tag!r}: error {worst:.3g} of the logit scale at {where}"
+
+
+@pytest.mark.parametrize("name,blocks", [("B", 3), ("C", 10)])
+def test_decode_steps_on_the_large_batch_kernel(name, blocks, tiny_models, references, tmp_path):
+    """The decode attention of large batches (key tiles dealt out over a fixed number of blocks), forced on
+    for these small ones: tails decoded one by one and mixed steps, captured graphs included."""
+    d, cfg, page = tiny_models[name]
+    seqs, ref = references[name]
+    families = {"t": helpers.trace_tail(seqs, tag="t"), "m": helpers.trace_mixed(seqs, tag="m")}
+    # four requests decoding together: one token each per step, for 40 steps after their prompts
+    together = []
+    keys = list(seqs)[-4:]
+    heads = {k: max(len(seqs[k]) - 40, 1) for k in keys}
+    together.append({"entries": [{"id": f"g{k}", "tokens": seqs[k][:heads[k]], "want": []} for k in keys], "end": []})
+    longest = max(len(seqs[k]) - heads[k] for k in keys)
+    for i in range(longest):
+        ent = [{"id": f"g{k}", "tokens": [seqs[k][heads[k] + i]], "want": [0]} for k in keys if heads[k] + i < len(seqs[k])]
+        end = [f"g{k}" for k in keys if heads[k] + i == len(seqs[k]) - 1]
+        together.append({"entries": ent, "end": end})
+    families["g"] = together
+    steps = [s for f in families.values() for s in f]
+    longest4 = sorted((len(v) for v in seqs.values()), reverse=True)[:4]
+    max_tokens = sum(-(-n // 64) * 64 for n in longest4)
+    steps, out = helpers.run_trace(d, "bfloat16", steps, str(tmp_path), max_tokens, page,
+                                   env={"ATOMA_INFER_DECODE_FLAT": str(blocks)})
+    for tag in families:
+        sub = [s for s in steps if s["entries"][0]["id"].startswith(tag)]
+        worst, where, agree = helpers.compare_trace(sub, out, cfg["vocab_size"], ref)
+        assert worst <= helpers.BF16_TOL, f"family {tag!r}: error {worst:.3g} of the logit scale at {where}"
