@@ -167,6 +167,10 @@ linear_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
     }
 }
 
+static int g_ksplit_override = 0;
+// For tuning: a fixed number of K splits (0: chosen from the number of tiles, as usual).
+extern "C" void linear_skinny_set_ksplit(int k) { g_ksplit_override = k; }
+
 // x [M, K] and w [N, K] bfloat16, rows 16-byte aligned (K % 8 == 0); M <= 16.
 extern "C" int linear_skinny(const void* x, const void* w, void* y, int out_dtype, int epilogue, const int* meta,
                              int use_rows, int M, int N, int K, cudaStream_t stream) {
@@ -181,6 +185,7 @@ extern "C" int linear_skinny(const void* x, const void* w, void* y, int out_dtyp
     // Too few tiles to fill the GPU: clusters of blocks split K (at least one 32-wide k block per warp each).
     int sms = 148;
     int ksplits = (2 * sms + tiles - 1) / tiles;
+    if (g_ksplit_override > 0) ksplits = g_ksplit_override;
     ksplits = max(1, min(min(ksplits, 8), ((K + 31) / 32) / SM_WARPS));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles, ksplits, 1);
