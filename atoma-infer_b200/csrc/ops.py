@@ -28,7 +28,7 @@ ATTENTION_SOURCES = ["kernels/attention_bf16.cu"]
 GEMM_SOURCES = ["kernels/gemm_tcgen05.cu"]
 ATTENTION_TC_SOURCES = ["kernels/attention_tcgen05.cu"]
 ATTENTION_TC_HEAD_DIMS = (64, 128)  # head sizes of the tcgen05 prefill attention
-ATTENTION_HEAD_DIMS = (16, 64, 128)  # built by the build check; other head sizes are built when a model needs them
+ATTENTION_HEAD_DIMS = tuple(range(16, 257, 16))  # every head size the kernels take; the build check builds them all, a model only its own
 
 
 class KernelError(RuntimeError):

@@ -126,6 +126,24 @@ def test_cluster_and_scratch_merges_agree_bitwise(rts):
     assert torch.equal(outs[0], outs[1])
 
 
+@pytest.mark.parametrize("d", list(range(16, 257, 16)))
+def test_every_head_size_bf16(rts, d):
+    """Head sizes in steps of 16 up to 256: portions of prompts, decode steps with fixed splits and with the
+    large-batch kernel."""
+    rt = rts["bfloat16"]
+    got, want = run_attention(rt, [(0, 70), (37, 29), (130, 2)], 4, 2, d, 16, seed=d)
+    assert worst(got, want) < 2e-2
+    decode = [(0, 1), (31, 1), (300, 1), (63, 1)]
+    got, want = run_attention(rt, decode, 4, 2, d, 16, seed=d, splits=3)
+    assert worst(got, want) < 2e-2
+    rt.ops._decode_flat_blocks = lambda *a: 5
+    try:
+        got, want = run_attention(rt, decode, 4, 2, d, 16, seed=d)
+    finally:
+        del rt.ops._decode_flat_blocks
+    assert worst(got, want) < 2e-2
+
+
 @pytest.mark.parametrize("window", [1, 5, 64, 100])
 def test_window_bf16_and_float32(rts, window):
     for dtype, tol in (("bfloat16", 2e-2), ("float32", 2e-5)):
