@@ -249,7 +249,6 @@ constexpr int DEC_NK = DEC_KT / 8;
 constexpr int DEC_WARPS = 4;
 constexpr int DEC_STAGES = D <= 128 ? 2 : 1;
 constexpr int DEC_WARP_ELEMS = DEC_STAGES * 2 * DEC_KT * LDS;  // bf16 elements of one warp's K/V stages
-constexpr size_t DEC_TILE_BYTES = (size_t)(16 * LDS + DEC_WARPS * DEC_WARP_ELEMS) * sizeof(bf16);
 constexpr size_t DEC_MERGE_BYTES = (size_t)DEC_WARPS * (32 + 16 * D) * sizeof(float);
 constexpr size_t DEC_MAIN_BYTES = 16 * LDS * sizeof(bf16) +
     (DEC_WARPS * DEC_WARP_ELEMS * sizeof(bf16) > DEC_MERGE_BYTES ? DEC_WARPS * DEC_WARP_ELEMS * sizeof(bf16) : DEC_MERGE_BYTES);
