@@ -69,6 +69,8 @@ MORE = {
     "d256g2": (_cfg(512, 777, 1000, 1, 2, 1, 1e-5, 10000.0, False), 64),
     "d112g8": (_cfg(896, 1024, 333, 1, 8, 1, 1e-5, 500000.0, True, scaling=(8.0, 4.0, 128)), 16),
     "d16g16": (_cfg(256, 384, 128, 2, 16, 1, 1e-5, 10000.0, False), 16),
+    # a head size that is no multiple of 16: the plain attention kernel serves bfloat16 too
+    "d24g2": (_cfg(96, 200, 150, 1, 4, 2, 1e-5, 10000.0, True), 8),
 }
 
 FP32_TOL = 2e-5   # times the largest |logit| of the sequence
