@@ -120,3 +120,24 @@ def test_decode_steps_on_the_large_batch_kernel(name, blocks, tiny_models, refer
         sub = [s for s in steps if s["entries"][0]["id"].startswith(tag)]
         worst, where, agree = helpers.compare_trace(sub, out, cfg["vocab_size"], ref)
         assert worst <= helpers.BF16_TOL, f"family {tag!r}: error {worst:.3g} of the logit scale at {where}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_long_prompt(dtype, tiny_models, tmp_path):
+    """2,040 tokens: whole (16 key tiles of 128 for the last query tile, the many-token rotation and norm
+    kernels), in three portions (each attending to what the earlier ones cached), then decoded tokens up to
+    the model's 2,048 positions."""
+    d, cfg, page = tiny_models["C"]
+    seq = helpers.random_tokens(cfg["vocab_size"], (2048,), seed=31)
+    (k, v), = seq.items()
+    ref = {k: P.forward(helpers.read_weights(d), cfg, v, compute=torch.float32)}
+    want = [0, 127, 128, 1000, 2039]
+    steps = [{"entries": [{"id": f"w{k}", "tokens": v[:2040], "want": want}], "end": [f"w{k}"]}]
+    cuts = [0, 700, 1500, 2040]
+    for a, b in zip(cuts, cuts[1:]):
+        steps.append({"entries": [{"id": f"c{k}", "tokens": v[a:b], "want": [0, b - a - 1]}], "end": []})
+    for i in range(2040, 2048):
+        steps.append({"entries": [{"id": f"c{k}", "tokens": [v[i]], "want": [0]}], "end": [f"c{k}"] if i == 2047 else []})
+    steps, out = helpers.run_trace(d, dtype, steps, str(tmp_path), 2048, page)
+    worst, where, agree = helpers.compare_trace(steps, out, cfg["vocab_size"], ref)
+    assert worst <= (5e-5 if dtype == "float32" else helpers.BF16_TOL), (worst, where)
