@@ -86,6 +86,30 @@ def test_preemption_by_recompute_keeps_tokens(tiny_models):
     assert tight.lm.manager.audit() == "" and tight.lm.manager.num_requests() == 0
 
 
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_many_requests_few_pages_small_budget(name, tiny_models):
+    """Twenty requests of mixed lengths through eight sequence slots, a token budget that cuts prompts into
+    portions beside decoding requests, and a page pool that forces preemptions: every request's greedy
+    tokens still equal the plain implementation's, and every page comes back."""
+    from atoma_infer_b200.sampling import SamplingParams
+
+    d, cfg, page = tiny_models[name]
+    w = helpers.read_weights(d)
+    g = torch.Generator().manual_seed(17)
+    lengths = torch.randint(1, 60, (20,), generator=g).tolist()
+    news = torch.randint(1, 18, (20,), generator=g).tolist()
+    prompts = list(helpers.random_tokens(cfg["vocab_size"], lengths, seed=9).values())
+    want = [P.generate_greedy(w, cfg, p, n) for p, n in zip(prompts, news)]
+    eng = _engine(d, page, "float32", num_gpu_blocks_override=(128 // page) + 1, max_num_sequences=8,
+                  max_num_batched_tokens=24)  # 128 tokens of cache for up to 8 x 77
+    params = [SamplingParams(do_sample=False, max_new_tokens=n, ignore_eos_token=True) for n in news]
+    outs = eng.generate(prompts, params)
+    assert [o.token_ids for o in outs] == want
+    assert eng.scheduler.num_preemptions > 0
+    assert eng.lm.manager.audit() == "" and eng.lm.manager.num_requests() == 0
+    assert eng.lm.manager.num_free_pages(0) == eng.lm.manager.num_usable_pages(0)
+
+
 def test_smoke_entry():
     import __graft_entry__ as g
 
