@@ -74,7 +74,8 @@ class CudaOps:
         # Programmatic dependent launch lets a kernel start while its predecessor drains (its weight
         # loads are in flight before the dependency wait).  Measured on the decode step of Llama 3.2 1B:
         # on for the few-row linears and the attention kernels 0.913 ms, off 0.967 ms, on for every
-        # kernel (norms included) 1.17 ms.  ATOMA_INFER_PDL: "0" off, "1" every kernel, default "linear".
+        # kernel 1.17 ms (it is the norm kernel as a dependent that costs: linears + attention + norm
+        # alone 1.19 ms).  ATOMA_INFER_PDL: "0" off, "1" every kernel, default "linear".
         mode = os.environ.get("ATOMA_INFER_PDL", "linear")
         self.pdl = {"0": 0, "1": 1, "linear": 2}.get(mode, 2)
         self.fused_rope = os.environ.get("ATOMA_INFER_FUSED_ROPE", "1") != "0"
