@@ -3,8 +3,9 @@
 Every function launches hand-written CUDA from the libraries under ``kernels/``
 on torch's current stream; tensors are only memory here.  There is no CPU path:
 without a CUDA device the constructor raises.  Matrix products of the bfloat16
-path with many rows go to cuBLAS through ``torch.matmul``, as the reference sends
-its linears to cuBLAS through candle (models/src/llama.rs:269-271).
+path with many rows go to cuBLAS through ``torch.mm``, as the reference sends
+its linears to cuBLAS through candle (models/src/llama.rs:269-271); the gate/up
+product of long prompts, with its activation, runs on the tcgen05 kernel here.
 """
 from __future__ import annotations
 
