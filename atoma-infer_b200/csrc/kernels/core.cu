@@ -56,7 +56,6 @@ add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, cons
                    const float* __restrict__ w, float eps, TO* __restrict__ out, const int* __restrict__ meta, int H,
                    int aligned) {
     __shared__ float red[33];
-    pdl_launch_dependents();
     constexpr int MAXV = 4;  // up to 4 x 4 values per thread stay in registers (H <= 16 * blockDim)
     // four values per access: rows start on multiples of four elements and the buffers on 16 bytes
     const bool in_regs = aligned && (H % 4 == 0) && H <= 4 * MAXV * (int)blockDim.x;
@@ -69,6 +68,9 @@ add_rmsnorm_kernel(float* __restrict__ resid, const TD* __restrict__ delta, cons
         }
     }
     pdl_wait();
+    // The kernels after this one may start now, not earlier: they fetch their weights and then wait for this
+    // kernel, and blocks that wait through the whole of the kernel before this one slow it down.
+    pdl_launch_dependents();
     int r = blockIdx.x;
     int limit = rows ? meta[META_NUM_ROWS] : meta[META_NUM_TOKENS];
     if (r >= limit) return;
@@ -183,8 +185,8 @@ extern "C" int add_rmsnorm(float* resid, const void* delta, int delta_dtype, con
 #undef ROWS_CASE
     }
 #define NORM_CASE(TD, TO) \
-    return (int)launch_kernel(add_rmsnorm_kernel<TD, TO>, n, threads, 0, stream, resid, (const TD*)delta, rows, w, eps, \
-                              (TO*)out, meta, H, aligned)
+    return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, add_rmsnorm_kernel<TD, TO>, n, threads, 0, stream, resid, (const TD*)delta, \
+                                  rows, w, eps, (TO*)out, meta, H, aligned)
     if (delta_dtype == DT_F32 && out_dtype == DT_F32) NORM_CASE(float, float);
     else if (delta_dtype == DT_BF16 && out_dtype == DT_BF16) NORM_CASE(__nv_bfloat16, __nv_bfloat16);
     else if (delta_dtype == DT_F32 && out_dtype == DT_BF16) NORM_CASE(float, __nv_bfloat16);

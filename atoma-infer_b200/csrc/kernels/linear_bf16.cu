@@ -92,9 +92,9 @@ linear_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
         }
     };
     int kb0 = kb_begin + warp * SM_UNROLL;
-    pdl_launch_dependents();
     if (kb0 < nblocks) load_weights(kb0);  // weights depend on no earlier kernel: in flight before the wait
     pdl_wait();                            // x is what the kernel before wrote
+    pdl_launch_dependents();
     while (kb0 < nblocks) {
         uint4 vx[SM_UNROLL][NT];
 #pragma unroll

@@ -73,12 +73,16 @@ class CudaOps:
         self.last_tokens = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # by state slot
         self._counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)  # split arrivals; kernels leave zeros
         # Programmatic dependent launch lets a kernel start while its predecessor drains (its weight
-        # loads are in flight before the dependency wait).  Measured on the decode step of Llama 3.2 1B:
-        # on for the few-row linears and the attention kernels 0.913 ms, off 0.967 ms, on for every
-        # kernel 1.17 ms (it is the norm kernel as a dependent that costs: linears + attention + norm
-        # alone 1.19 ms).  ATOMA_INFER_PDL: "0" off, "1" every kernel, default "linear".
-        mode = os.environ.get("ATOMA_INFER_PDL", "linear")
-        self.pdl = {"0": 0, "1": 1, "linear": 2}.get(mode, 2)
+        # loads are in flight before the dependency wait).  Blocks that have started early wait for the
+        # kernel before them and slow it down while they do, so only kernels whose wait is short start
+        # early: the few-row linears and the decode attention release their dependents when they start
+        # themselves; the norm kernel, which also starts early, releases its dependents only once its own
+        # wait is over (else the linear after it would wait through the whole linear before it).  Measured
+        # on the decode step of Llama 3.2 1B: off 0.967 ms; linears and attention 0.918 ms; with the norm
+        # 0.906 ms; every kernel, each releasing its dependents at once, 1.17 ms.
+        # ATOMA_INFER_PDL: "0" off, "1" every kernel, "linear" without the norm, default "linear+norm".
+        mode = os.environ.get("ATOMA_INFER_PDL", "linear+norm")
+        self.pdl = {"0": 0, "1": 1, "linear": 2, "linear+norm": 6}.get(mode, 6)
         self.fused_rope = os.environ.get("ATOMA_INFER_FUSED_ROPE", "1") != "0"
         self.lib.kernels_set_pdl(int(self.pdl))
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
