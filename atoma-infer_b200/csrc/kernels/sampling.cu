@@ -61,7 +61,18 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
 
     // argmax of the logits, lowest index among equals
     ArgMax best{-INFINITY, 0x7fffffff};
-    for (int i = tid; i < V; i += SAMPLE_THREADS) best = better(best, ArgMax{row[i], i});
+    if (V % 4 == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {  // four logits a load
+        const float4* row4 = reinterpret_cast<const float4*>(row);
+        for (int i = tid; i < V / 4; i += SAMPLE_THREADS) {
+            const float4 v = row4[i];
+            best = better(best, ArgMax{v.x, 4 * i});
+            best = better(best, ArgMax{v.y, 4 * i + 1});
+            best = better(best, ArgMax{v.z, 4 * i + 2});
+            best = better(best, ArgMax{v.w, 4 * i + 3});
+        }
+    } else {
+        for (int i = tid; i < V; i += SAMPLE_THREADS) best = better(best, ArgMax{row[i], i});
+    }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         ArgMax other{__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
