@@ -52,8 +52,8 @@ sample_rows_kernel(const float* __restrict__ logits, int V, const float* __restr
     __shared__ ArgMax amax[32];
     __shared__ int found, last_kept;
     __shared__ float target_s;
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (num_rows && r >= *num_rows) return;
     const float* row = logits + (size_t)r * V;
@@ -180,7 +180,7 @@ extern "C" int sample_rows(const float* logits, int R, int V, const float* tempe
                            const float* top_p, const unsigned long long* seed, const unsigned long long* step,
                            int* out, const int* num_rows, const int* slots, int* last_tokens, cudaStream_t stream) {
     if (R <= 0) return 0;
-    return (int)launch_kernel(sample_rows_kernel, R, SAMPLE_THREADS, 0, stream, logits, V, temperature, top_k, top_p, seed,
+    return (int)launch_kernel_pdl((g_use_pdl & 5) != 0, sample_rows_kernel, R, SAMPLE_THREADS, 0, stream, logits, V, temperature, top_k, top_p, seed,
                               step, out, num_rows, slots, last_tokens);
 }
 
