@@ -32,8 +32,11 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, stream: IO
         raise ValueError(f"page size {page_size} neither divides nor is a multiple of {ROUND_TOKENS}")
     unit = max(ROUND_TOKENS, page_size)
     num_pages = ((max_tokens + unit - 1) // unit) * unit // page_size
+    # A replayed request may be as long as the pool is large: rotation angles are computed from the position,
+    # not looked up, so nothing ends at the configuration's max_position_embeddings (generation stops there).
     lm = load_model(model_dir, dtype=dtype, device=device, page_size=page_size, num_pages=num_pages,
-                    max_seqs=max_live, poison_cache=True, ops=ops, cuda_graphs=True)
+                    max_seqs=max_live, poison_cache=True, ops=ops, cuda_graphs=True,
+                    max_model_len=num_pages * page_size)
     ids: Dict[str, int] = {}
     next_id = 0
     steps = 0

@@ -141,3 +141,16 @@ def test_a_long_prompt(dtype, tiny_models, tmp_path):
     steps, out = helpers.run_trace(d, dtype, steps, str(tmp_path), 2048, page)
     worst, where, agree = helpers.compare_trace(steps, out, cfg["vocab_size"], ref)
     assert worst <= (5e-5 if dtype == "float32" else helpers.BF16_TOL), (worst, where)
+
+
+def test_replay_beyond_the_configured_positions(tmp_path):
+    """A request longer than max_position_embeddings replays (positions are not table rows here) and still
+    equals the plain implementation."""
+    cfg = dict(helpers.CONFIG_A, max_position_embeddings=32)
+    d = helpers.make_model(str(tmp_path / "model"), cfg, seed=3)
+    seqs = helpers.random_tokens(cfg["vocab_size"], (90,), seed=2)
+    ref = {k: P.forward(helpers.read_weights(d), cfg, v) for k, v in seqs.items()}
+    steps = helpers.trace_tail(seqs, tail=40)
+    steps, out = helpers.run_trace(d, "float32", steps, str(tmp_path / "out"), 128, 4)
+    worst, where, agree = helpers.compare_trace(steps, out, cfg["vocab_size"], ref)
+    assert worst <= helpers.FP32_TOL and agree == 1.0, (worst, where)
