@@ -2,7 +2,7 @@
 
 The reference picks its model at compile time (a cargo feature and a generic
 parameter, server/src/main.rs:45, backends/src/lib.rs:10-13).  Here the name in
-``config.json``'s ``architectures[0]`` picks an ``Architecture`` at run time, and
+``config.json``'s ``architectures[0]`` (or, failing that, its ``model_type``) picks an ``Architecture`` at run time, and
 each layer of the model spec an architecture returns names its parts by kind
 ("attention", "swiglu", "rmsnorm", "rope", "prenorm"), which these tables resolve.
 Another architecture or another part is added by one ``register_*`` call from any
@@ -33,10 +33,17 @@ _PARTS: Dict[str, Dict[str, type]] = {
 }
 
 
-def register_architecture(name: str, parse_config, build_spec, *, replace: bool = False) -> None:
+_MODEL_TYPES: Dict[str, str] = {}  # config.json "model_type" -> architecture name, for folders without "architectures"
+
+
+def register_architecture(name: str, parse_config, build_spec, *, replace: bool = False, model_type: str = "") -> None:
+    """``model_type``: the value of config.json's ``model_type`` that also means this architecture (used only
+    when the file has no ``architectures`` list)."""
     if name in _ARCHITECTURES and not replace:
         raise ConfigError(f"architecture {name!r} is already registered")
     _ARCHITECTURES[name] = Architecture(name, parse_config, build_spec)
+    if model_type:
+        _MODEL_TYPES[model_type] = name
 
 
 def architecture(name: str) -> Architecture:
@@ -60,9 +67,14 @@ def architecture_of(model_dir: str):
     with open(path) as f:
         raw = json.load(f)
     archs = raw.get("architectures")
-    if not archs or not isinstance(archs, list):
-        raise ConfigError("config.json has no 'architectures' list; cannot choose a model")
-    arch = architecture(str(archs[0]))
+    if archs and isinstance(archs, list):
+        name = str(archs[0])
+    elif raw.get("model_type") in _MODEL_TYPES:
+        name = _MODEL_TYPES[raw["model_type"]]
+    else:
+        raise ConfigError("config.json has no 'architectures' list and no known 'model_type' "
+                          f"(known architectures: {sorted(_ARCHITECTURES)}; model types: {sorted(_MODEL_TYPES)})")
+    arch = architecture(name)
     return arch, arch.parse_config(raw)
 
 

@@ -36,4 +36,4 @@ def llama_spec(cfg: LlamaConfig) -> ModelSpec:
     )
 
 
-register_architecture("LlamaForCausalLM", LlamaConfig.from_dict, llama_spec)
+register_architecture("LlamaForCausalLM", LlamaConfig.from_dict, llama_spec, model_type="llama")

@@ -73,6 +73,14 @@ def test_registry_chooses_by_architecture_name(tmp_path):
     assert "NopeForCausalLM" in str(e.value) and "LlamaForCausalLM" in str(e.value)
     with pytest.raises(ConfigError):
         register_architecture("LlamaForCausalLM", dict, dict)
+    # a folder without an "architectures" list: its model_type chooses; neither: one clear error
+    bare = {k: v for k, v in helpers.CONFIG_B.items() if k != "architectures"}
+    (tmp_path / "config.json").write_text(json.dumps(dict(bare, model_type="llama")))
+    assert architecture_of(str(tmp_path))[0].name == "LlamaForCausalLM"
+    (tmp_path / "config.json").write_text(json.dumps(bare))
+    with pytest.raises(ConfigError) as e:
+        architecture_of(str(tmp_path))
+    assert "architectures" in str(e.value) and "model_type" in str(e.value)
 
 
 def test_engine_config_checks_and_toml(tmp_path):
