@@ -59,7 +59,8 @@ def _bind(lib):
         "sched_create": (c.c_void_p, [c.c_void_p, c.c_int, c.c_int, i64, c.c_int]),
         "sched_destroy": (None, [c.c_void_p]),
         "sched_add_request": (c.c_int, [c.c_void_p, i64, i64]),
-        "sched_schedule": (c.c_int, [c.c_void_p, c.c_int, i64p, i64p, i32p, i32p, i32p, i64p, i64p, i32p]),
+        "sched_schedule": (c.c_int, [c.c_void_p, i32p]),
+        "sched_plan": (c.c_int, [c.c_void_p, i64p, i64p, i32p, i32p, i32p, i64p, i64p]),
         "sched_step_done": (None, [c.c_void_p]),
         "sched_append_token": (c.c_int, [c.c_void_p, i64]),
         "sched_finish": (c.c_int, [c.c_void_p, i64]),

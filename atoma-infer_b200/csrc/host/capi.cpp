@@ -57,23 +57,39 @@ int cm_audit(void* h, char* out, int cap) {
     return (int)s.size();
 }
 
+// A scheduler handle keeps the last plan, so that planning (which changes the queues) and
+// copying the plan out (which needs arrays of the right size) are two calls and the second
+// cannot fail after the first has acted.
+struct SchedulerHandle {
+    Scheduler scheduler;
+    StepPlan plan;
+    SchedulerHandle(CacheManager* cache, const SchedulerConfig& cfg) : scheduler(cache, cfg) {}
+};
+static Scheduler* sched(void* h) { return &static_cast<SchedulerHandle*>(h)->scheduler; }
+
 void* sched_create(void* cache, int max_num_batched_tokens, int max_num_seqs, int64_t max_model_len,
                    int enable_chunked_prefill) {
     if (!cache || max_num_batched_tokens <= 0 || max_num_seqs <= 0 || max_model_len <= 0) return nullptr;
     SchedulerConfig cfg{max_num_batched_tokens, max_num_seqs, max_model_len, enable_chunked_prefill};
-    return new (std::nothrow) Scheduler(static_cast<CacheManager*>(cache), cfg);
+    return new (std::nothrow) SchedulerHandle(static_cast<CacheManager*>(cache), cfg);
 }
-void sched_destroy(void* h) { delete static_cast<Scheduler*>(h); }
-int sched_add_request(void* h, int64_t req, int64_t prompt_len) {
-    return static_cast<Scheduler*>(h)->add_request(req, prompt_len);
+void sched_destroy(void* h) { delete static_cast<SchedulerHandle*>(h); }
+int sched_add_request(void* h, int64_t req, int64_t prompt_len) { return sched(h)->add_request(req, prompt_len); }
+// Plans a step and keeps the plan in the handle.  counts[0..2] = entries, preempted, ignored:
+// the sizes of the arrays that sched_plan fills.
+int sched_schedule(void* h, int32_t* counts) {
+    auto* sh = static_cast<SchedulerHandle*>(h);
+    sh->plan = sh->scheduler.schedule();
+    counts[0] = (int)sh->plan.entries.size();
+    counts[1] = (int)sh->plan.preempted.size();
+    counts[2] = (int)sh->plan.ignored.size();
+    return engine::kOk;
 }
-// Plans a step.  Entries go to the five arrays (capacity `cap`); preempted and
-// ignored request ids to theirs.  counts[0..2] = entries, preempted, ignored.
-int sched_schedule(void* h, int cap, int64_t* req, int64_t* context_len, int32_t* num_tokens, int32_t* samples,
-                   int32_t* is_prompt, int64_t* preempted, int64_t* ignored, int32_t* counts) {
-    StepPlan plan = static_cast<Scheduler*>(h)->schedule();
-    if ((int)plan.entries.size() > cap || (int)plan.preempted.size() > cap || (int)plan.ignored.size() > cap)
-        return engine::kErrArgument;
+// Copies the plan of the last sched_schedule: entries to the five arrays, preempted and ignored
+// request ids to theirs (each at least as long as the count sched_schedule gave).
+int sched_plan(void* h, int64_t* req, int64_t* context_len, int32_t* num_tokens, int32_t* samples,
+               int32_t* is_prompt, int64_t* preempted, int64_t* ignored) {
+    const StepPlan& plan = static_cast<SchedulerHandle*>(h)->plan;
     for (size_t i = 0; i < plan.entries.size(); ++i) {
         req[i] = plan.entries[i].req;
         context_len[i] = plan.entries[i].context_len;
@@ -83,20 +99,17 @@ int sched_schedule(void* h, int cap, int64_t* req, int64_t* context_len, int32_t
     }
     for (size_t i = 0; i < plan.preempted.size(); ++i) preempted[i] = plan.preempted[i];
     for (size_t i = 0; i < plan.ignored.size(); ++i) ignored[i] = plan.ignored[i];
-    counts[0] = (int)plan.entries.size();
-    counts[1] = (int)plan.preempted.size();
-    counts[2] = (int)plan.ignored.size();
     return engine::kOk;
 }
-void sched_step_done(void* h) { static_cast<Scheduler*>(h)->step_done(); }
-int sched_append_token(void* h, int64_t req) { return static_cast<Scheduler*>(h)->append_token(req); }
-int sched_finish(void* h, int64_t req) { return static_cast<Scheduler*>(h)->finish(req); }
-int sched_status(void* h, int64_t req) { return static_cast<Scheduler*>(h)->status(req); }
-int64_t sched_length(void* h, int64_t req) { return static_cast<Scheduler*>(h)->length(req); }
-int64_t sched_num_computed(void* h, int64_t req) { return static_cast<Scheduler*>(h)->num_computed(req); }
-int sched_num_waiting(void* h) { return static_cast<Scheduler*>(h)->num_waiting(); }
-int sched_num_running(void* h) { return static_cast<Scheduler*>(h)->num_running(); }
-int64_t sched_num_preemptions(void* h) { return static_cast<Scheduler*>(h)->num_preemptions(); }
-int64_t sched_prompt_limit(void* h) { return static_cast<Scheduler*>(h)->prompt_limit(); }
+void sched_step_done(void* h) { sched(h)->step_done(); }
+int sched_append_token(void* h, int64_t req) { return sched(h)->append_token(req); }
+int sched_finish(void* h, int64_t req) { return sched(h)->finish(req); }
+int sched_status(void* h, int64_t req) { return sched(h)->status(req); }
+int64_t sched_length(void* h, int64_t req) { return sched(h)->length(req); }
+int64_t sched_num_computed(void* h, int64_t req) { return sched(h)->num_computed(req); }
+int sched_num_waiting(void* h) { return sched(h)->num_waiting(); }
+int sched_num_running(void* h) { return sched(h)->num_running(); }
+int64_t sched_num_preemptions(void* h) { return sched(h)->num_preemptions(); }
+int64_t sched_prompt_limit(void* h) { return sched(h)->prompt_limit(); }
 
 }  // extern "C"

@@ -34,20 +34,11 @@ class Scheduler:
                  max_model_len: int, enable_chunked_prefill: bool = True):
         self._lib = native()
         self.cache = cache  # keeps the native cache manager alive
-        self._cap = max(max_num_seqs, 1) + 8
         self._h = self._lib.sched_create(cache.handle, max_num_batched_tokens, max_num_seqs, max_model_len,
                                          int(enable_chunked_prefill))
         if not self._h:
             raise ValueError("scheduler: budgets and max_model_len must be positive")
-        c = ctypes
-        self._req = (c.c_int64 * self._cap)()
-        self._ctx = (c.c_int64 * self._cap)()
-        self._n = (c.c_int32 * self._cap)()
-        self._samples = (c.c_int32 * self._cap)()
-        self._is_prompt = (c.c_int32 * self._cap)()
-        self._pre = (c.c_int64 * self._cap)()
-        self._ign = (c.c_int64 * self._cap)()
-        self._counts = (c.c_int32 * 3)()
+        self._counts = (ctypes.c_int32 * 3)()
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
@@ -60,14 +51,19 @@ class Scheduler:
             raise CacheError(code, f"scheduler.add_request({req}, {prompt_len})")
 
     def schedule(self) -> StepPlan:
-        code = self._lib.sched_schedule(self._h, self._cap, self._req, self._ctx, self._n, self._samples,
-                                        self._is_prompt, self._pre, self._ign, self._counts)
+        """Plans one step.  Planning changes the queues, so it cannot be allowed to fail afterwards: the
+        native side keeps the plan and says how long its three lists are, then fills arrays of that size."""
+        code = self._lib.sched_schedule(self._h, self._counts)
         if code < 0:
             raise CacheError(code, "scheduler.schedule")
         ne, npre, nign = self._counts[0], self._counts[1], self._counts[2]
-        entries = [PlannedEntry(self._req[i], self._ctx[i], self._n[i], bool(self._samples[i]), bool(self._is_prompt[i]))
-                   for i in range(ne)]
-        return StepPlan(entries, list(self._pre[:npre]), list(self._ign[:nign]))
+        c = ctypes
+        i64 = lambda n: (c.c_int64 * max(n, 1))()  # noqa: E731
+        i32 = lambda n: (c.c_int32 * max(n, 1))()  # noqa: E731
+        req, ctx, num, samples, is_prompt, pre, ign = i64(ne), i64(ne), i32(ne), i32(ne), i32(ne), i64(npre), i64(nign)
+        self._lib.sched_plan(self._h, req, ctx, num, samples, is_prompt, pre, ign)
+        entries = [PlannedEntry(req[i], ctx[i], num[i], bool(samples[i]), bool(is_prompt[i])) for i in range(ne)]
+        return StepPlan(entries, list(pre[:npre]), list(ign[:nign]))
 
     def step_done(self) -> None:
         self._lib.sched_step_done(self._h)

@@ -142,3 +142,31 @@ def test_abort_from_either_queue_frees_everything():
     assert cm.num_free_pages() == 8 and cm.num_requests() == 0 and cm.audit() == ""
     with pytest.raises(Exception):
         s.finish(0)
+
+
+def test_many_ignored_requests_in_one_step_do_not_lose_the_plan():
+    """Forty prompts beyond the model length wait in front of two that fit, with four sequence slots: the
+    step that drops the forty (backends/vllm/src/scheduler.rs:957-992 marks them ignored) still returns
+    its whole plan, the two prompts run, and the scheduler forgets the dropped ones."""
+    cm, s = make(pages=16, budget=32, seqs=4, model_len=12)
+    for r in range(40):
+        s.add_request(r, 13 + r % 5)
+    s.add_request(100, 5)
+    s.add_request(101, 12)
+    p = run_step(cm, s)
+    assert sorted(p.ignored) == list(range(40))
+    assert summary(p) == [(100, 5, True), (101, 12, True)]
+    assert all(s.status(r) == UNKNOWN for r in range(40))
+    assert s.num_waiting == 0 and s.num_running == 2
+    p = run_step(cm, s, finish=(100, 101))
+    assert summary(p) == [(100, 1, True), (101, 1, True)] and not p.ignored
+    assert cm.num_requests() == 0 and cm.num_free_pages(0) == cm.num_usable_pages(0)
+
+
+def test_prompts_that_no_empty_cache_could_hold_are_ignored_in_any_number():
+    cm, s = make(pages=4, budget=64, seqs=2, model_len=64)  # 16 tokens of cache
+    for r in range(30):
+        s.add_request(r, 17 + r)
+    s.add_request(99, 16)
+    p = run_step(cm, s)
+    assert sorted(p.ignored) == list(range(30)) and summary(p) == [(99, 16, True)]
