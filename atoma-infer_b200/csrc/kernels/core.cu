@@ -22,13 +22,14 @@ extern "C" void kernels_set_pdl(int mode) { g_use_pdl = mode; }
 template <typename T>
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
                                   float* __restrict__ resid, const int* __restrict__ meta, int H, int V,
-                                  const int* __restrict__ last_tokens, int* __restrict__ status) {
+                                  const int* __restrict__ last_tokens, int num_slots, int* __restrict__ status) {
     pdl_launch_dependents();
     pdl_wait();
     int t = blockIdx.x;
     if (t >= meta[META_NUM_TOKENS]) return;
     int tok = tokens[t];
-    if (tok < 0 && last_tokens) tok = last_tokens[-tok - 1];
+    // a slot beyond the array leaves the id negative, which is reported as a bad token below
+    if (tok < 0 && last_tokens && -(long long)tok - 1 < num_slots) tok = last_tokens[-tok - 1];
     bool bad = tok < 0 || tok >= V;
     if (bad && threadIdx.x == 0) atomicExch(&status[STATUS_BAD_TOKEN], 1 + t);
     const T* row = table + (size_t)(bad ? 0 : tok) * H;
@@ -37,14 +38,14 @@ __global__ void embed_rows_kernel(const int* __restrict__ tokens, const T* __res
 }
 
 extern "C" int embed_rows(const int* tokens, const void* table, int table_dtype, float* resid, const int* meta,
-                          int T, int H, int V, const int* last_tokens, int* status, cudaStream_t stream) {
+                          int T, int H, int V, const int* last_tokens, int num_slots, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
     int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == DT_F32)
         return (int)launch_kernel(embed_rows_kernel<float>, T, threads, 0, stream, tokens, (const float*)table, resid, meta, H, V, last_tokens,
-                                  status);
+                                  num_slots, status);
     return (int)launch_kernel(embed_rows_kernel<__nv_bfloat16>, T, threads, 0, stream, tokens, (const __nv_bfloat16*)table, resid,
-                              meta, H, V, last_tokens, status);
+                              meta, H, V, last_tokens, num_slots, status);
 }
 
 // ----------------------------------------------------------------------------- RMSNorm

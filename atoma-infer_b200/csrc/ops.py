@@ -102,24 +102,35 @@ class CudaOps:
         for lib in self._attn_libs.values():
             lib.kernels_set_pdl(1 if on else 0)
 
+    @staticmethod
+    def describe_status(words) -> Optional[str]:
+        """What the status words say (None: nothing).  Kernels write them instead of trapping or hanging."""
+        s = list(words)
+        if not any(s):
+            return None
+        return (f"token id out of range at token {s[0] - 1}" if s[0] else
+                f"block table names no valid page for token {s[1] - 1}" if s[1] else
+                f"a tensor-core GEMM block ({s[2] - 1}) gave up waiting on a barrier" if s[2] else
+                f"a tensor-core attention block ({s[3] - 1}) gave up waiting on a barrier")
+
+    def clear_status(self) -> None:
+        self.status.zero_()
+
     def check_status(self) -> None:
-        """Raises if a kernel of an earlier launch met a bad token id or page id (synchronises)."""
-        s = self.status.tolist()
-        if any(s):
-            self.status.zero_()
-            raise KernelError(
-                f"device status: token id out of range at token {s[0] - 1}" if s[0] else
-                f"device status: block table names no valid page for token {s[1] - 1}" if s[1] else
-                f"device status: a tensor-core GEMM block ({s[2] - 1}) gave up waiting on a barrier" if s[2] else
-                f"device status: a tensor-core attention block ({s[3] - 1}) gave up waiting on a barrier"
-            )
+        """Raises if a kernel of an earlier launch met a bad token id or page id, or gave up a wait
+        (synchronises)."""
+        what = self.describe_status(self.status.tolist())
+        if what:
+            self.clear_status()
+            raise KernelError("device status: " + what)
 
     # ------------------------------------------------------------------ kernels
     def embed(self, tokens, table, resid, meta, T: int):
         """A token id -1 - s means: the token last sampled into slot s (``self.last_tokens``)."""
         H, V = table.shape[1], table.shape[0]
         self._check(self.lib.embed_rows(_p(tokens), _p(table), _code(table), _p(resid), _p(meta), T, H, V,
-                                        _p(self.last_tokens), _p(self.status), self._stream()), "embed_rows")
+                                        _p(self.last_tokens), self.last_tokens.numel(), _p(self.status), self._stream()),
+                    "embed_rows")
 
     def add_rmsnorm(self, resid, delta, w, eps: float, out, meta, n: int, rows=None):
         """resid += delta (if given); out = rmsnorm(resid) * w.  With ``rows`` the sum and the

@@ -11,6 +11,7 @@ text is outside this engine.  A finished request's pages are given back at once.
 """
 from __future__ import annotations
 
+import sys
 import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Union
@@ -40,8 +41,9 @@ class RequestOutput:
     request_id: int
     prompt_token_ids: List[int]
     token_ids: List[int]
-    finish_reason: str  # "stop" (end-of-sequence or stop id), "length", "ignored"
+    finish_reason: str  # "stop" (end-of-sequence or stop id), "length", "ignored", "error"
     metrics: RequestMetrics
+    error: Optional[str] = None  # with "error": what the kernels reported for the step that spoilt the request
 
 
 @dataclass
@@ -69,7 +71,8 @@ class _Request:
 
 
 class Engine:
-    def __init__(self, model_dir: str, config: Optional[EngineConfig] = None, **overrides):
+    def __init__(self, model_dir: str, config: Optional[EngineConfig] = None, *, ops=None, **overrides):
+        """``ops``: another kernel table than the CUDA one (tests drive the host side with a stand-in)."""
         cfg = config or EngineConfig(**overrides)
         if config is not None and overrides:
             for k, v in overrides.items():
@@ -77,7 +80,8 @@ class Engine:
             cfg.__post_init__()
         self.config = cfg
         self.lm: LoadedModel = load_model(
-            model_dir, dtype=cfg.dtype, device=f"cuda:{cfg.device_id}", page_size=cfg.block_size,
+            model_dir, dtype=cfg.dtype, device=getattr(ops, "device", None) or f"cuda:{cfg.device_id}", ops=ops,
+            page_size=cfg.block_size,
             num_pages=cfg.num_gpu_blocks_override, max_seqs=cfg.max_num_sequences,
             gpu_memory_utilization=cfg.gpu_memory_utilization, cuda_graphs=cfg.cuda_graphs,
             max_model_len=cfg.max_model_len)
@@ -89,7 +93,8 @@ class Engine:
         self.sampler = Sampler(self.lm.rt)
         self.eos_token_ids = tuple(spec.eos_token_ids)
         self._requests: Dict[int, _Request] = {}
-        self._inflight = None  # (requests sampled, their tokens on the way to the host, event) of the last step
+        self._inflight = None  # (requests sampled, their tokens on the way to the host, all requests) of the last step
+        self.num_device_errors = 0
         self._next_id = 0
         self.num_steps = 0
         self.num_generated = 0
@@ -157,7 +162,7 @@ class Engine:
             if r.pending and e.context_len + e.num_tokens > known and not (e.num_tokens == 1 and e.context_len == known):
                 finished += self._resolve()
                 break
-        entries, sampled = [], []
+        entries, sampled, taking_part = [], [], []
         for e in plan.entries:
             r = self._requests.get(e.req)
             if r is None:  # ended while the tokens were read just above
@@ -169,6 +174,7 @@ class Engine:
             else:
                 toks = r.token_span(e.context_len, e.num_tokens)
             entries.append(StepEntry(e.req, toks, [e.num_tokens - 1] if e.samples else []))
+            taking_part.append(r)
             if e.samples:
                 sampled.append(r)
         if not entries:
@@ -180,7 +186,7 @@ class Engine:
         previous, self._inflight = self._inflight, None
         if sampled:
             slots = [self.lm.manager.state_slot(r.req) for r in sampled]
-            tokens, event = self.sampler.sample(
+            tokens = self.sampler.sample(
                 logits, [r.params for r in sampled], [len(r.output) + r.pending for r in sampled],
                 [r.tokens if r.params.repetition_penalty != 1.0 else () for r in sampled], slots=slots, defer=True)
             for r in sampled:
@@ -191,7 +197,7 @@ class Engine:
                     r.ends_by_count = True       # whatever the token is, the request ends with it
                 else:
                     self.scheduler.append_token(r.req)
-            self._inflight = (sampled, tokens, event)
+            self._inflight = (sampled, tokens, taking_part)
         finished += self._resolve(previous)
         if self._inflight and any(r.params.repetition_penalty != 1.0 for r in self._inflight[0]):
             finished += self._resolve()
@@ -203,11 +209,29 @@ class Engine:
             inflight, self._inflight = self._inflight, None
         if not inflight:
             return []
-        sampled, tokens, event = inflight
-        event.synchronize()
+        sampled, deferred, taking_part = inflight
+        tokens, status = deferred.wait()
         now = time.time()
         finished = []
-        for r, tok in zip(sampled, tokens.tolist()):
+        ops = self.lm.rt.ops
+        what = ops.describe_status(status) if status and hasattr(ops, "describe_status") else None
+        if what:
+            # A kernel reported a fault (a wait it gave up, a page or token id out of range) instead of
+            # hanging or trapping: what this step computed, and left in the cache, cannot be trusted.  Its
+            # requests end with reason "error"; the word is cleared for the steps that follow.
+            ops.clear_status()
+            self.num_device_errors += 1
+            print(f"[engine] device status: {what}; {len(taking_part)} requests of the step end with an error",
+                  file=sys.stderr, flush=True)
+            for r in taking_part:
+                if self._requests.get(r.req) is not r:
+                    continue
+                self.scheduler.finish(r.req)
+                r.metrics.finished_time = now
+                del self._requests[r.req]
+                finished.append(RequestOutput(r.req, r.prompt, r.output, "error", r.metrics, error=what))
+            return finished
+        for r, tok in zip(sampled, tokens):
             if self._requests.get(r.req) is not r:
                 continue  # ended or aborted since: its extra token is dropped
             r.pending -= 1

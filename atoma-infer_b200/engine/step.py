@@ -87,6 +87,7 @@ class StepFunction:
         ``pad_to``: lay the arrays out for that many tokens, entries and rows (a captured graph's
         fixed sizes); the header still holds the true counts, which is what the kernels obey."""
         mgr, ps = self.manager, self.page_size
+        vocab = self.model.spec.vocab_size
         infos: List[EntryInfo] = []
         seen = set()
         start = 0
@@ -102,14 +103,19 @@ class StepFunction:
             ctx_len = mgr.num_tokens(e.req)
             is_new = ctx_len == 0  # also a request that a scheduler admitted (again) and that has run nothing yet
             try:
+                for w in e.want:
+                    if not (0 <= w < n):
+                        raise ValueError(f"request {e.req}: wanted place {w} is outside its {n} tokens")
+                # token ids: in the vocabulary, or the one negative id that means "the token the sampler
+                # left on the device for this request's slot" (a single decode token)
+                lo, hi = min(e.tokens), max(e.tokens)
+                if hi >= vocab or (lo < 0 and not (n == 1 and ctx_len > 0 and lo == -1 - slot)):
+                    raise ValueError(f"request {e.req}: token ids must lie in [0, {vocab})")
                 mgr.reserve(e.req, ctx_len + n)
             except Exception:
                 if added:
                     mgr.free_request(e.req)
                 raise
-            for w in e.want:
-                if not (0 <= w < n):
-                    raise ValueError(f"request {e.req}: wanted place {w} is outside its {n} tokens")
             infos.append(EntryInfo(e.req, start, n, ctx_len, slot, is_new))
             start += n
         T, S = start, len(infos)

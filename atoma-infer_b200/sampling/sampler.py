@@ -26,11 +26,11 @@ class Sampler:
         """``logits`` [R, vocab] float32 on the device; ``steps[i]``: how many tokens request i
         has sampled before; ``histories[i]``: its tokens so far (for the repetition penalty);
         ``slots[i]``: where to leave the token on the device for the next step's embedding.
-        Returns the token ids as a list, or with ``defer`` as a pinned host tensor whose copy is
-        still in flight together with the CUDA event that marks its arrival."""
+        Returns the token ids as a list, or with ``defer`` a ``DeferredTokens``: the ids and the kernels'
+        status words on their way to pinned host memory, with the CUDA event that marks their arrival."""
         R = logits.shape[0]
         if R == 0:
-            return ([], None) if defer else []
+            return DeferredTokens(None, None, 0) if defer else []
         ops, dev = self.rt.ops, self.rt.device
         for i, p in enumerate(params):
             if p.repetition_penalty != 1.0:
@@ -55,8 +55,30 @@ class Sampler:
                    d[0:2 * R], d[2 * R:4 * R], out, slots=d[7 * R:8 * R] if S else None)
         if not defer:
             return out.tolist()
-        back = torch.empty(R, dtype=torch.int32, pin_memory=self._pinned)
-        back.copy_(out, non_blocking=True)
-        event = torch.cuda.Event()
-        event.record()
-        return back, event
+        status = getattr(ops, "status", None)
+        ns = status.numel() if status is not None else 0
+        back = torch.empty(R + ns, dtype=torch.int32, pin_memory=self._pinned)
+        back[:R].copy_(out, non_blocking=True)
+        if ns:  # the status words ride along: the host sees a kernel's complaint with the tokens it spoilt
+            back[R:].copy_(status, non_blocking=True)
+        event = None
+        if torch.cuda.is_available() and dev.type == "cuda":
+            event = torch.cuda.Event()
+            event.record()
+        return DeferredTokens(back, event, R)
+
+
+class DeferredTokens:
+    """Sampled token ids (and the kernels' status words) whose copy to the host may still be in flight."""
+
+    def __init__(self, host, event, num_rows: int):
+        self._host, self._event, self._rows = host, event, num_rows
+
+    def wait(self):
+        """(token ids as a list, status words as a list); blocks until the copy has landed."""
+        if self._host is None:
+            return [], []
+        if self._event is not None:
+            self._event.synchronize()
+        values = self._host.tolist()
+        return values[:self._rows], values[self._rows:]
