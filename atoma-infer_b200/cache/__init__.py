@@ -1,3 +1,3 @@
-from .spec import FULL_KEYS, WINDOW_KEYS, CacheGroup, CacheNeed, LayerCache
+from .spec import FULL_KEYS, WINDOW_KEYS, CachedTensor, CacheGroup, CacheNeed, LayerCache
 from .manager import CacheError, CacheManager, OutOfPages
-from .kv_cache import KVCache, page_bytes, pages_for_memory
+from .kv_cache import KVCache, page_bytes, pages_for_memory, state_bytes_total

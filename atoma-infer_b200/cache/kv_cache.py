@@ -1,9 +1,11 @@
-"""Device memory of the cache: pages of keys and values per group, state slots per layer.
+"""Device memory of the cache: pages per group, state slots per layer.
 
-One tensor per cache group, ``[layers_in_group, num_pages, 2, kv_heads, page_size,
-head_dim]``: a page id addresses the same page in every layer of its group (a layer here is
-a run of the model's schedule that owns a cache), and the
-(page, K|V, head) block of page_size * head_dim elements is contiguous.  The
+One tensor per cache group, ``[layers_in_group, num_pages, elements of a page]``: a page id addresses
+the same page in every layer of its group (a layer here is a run of the model's schedule that owns a
+cache).  Inside a page the named tensors of the group's need follow one another, each as
+``[heads, page_size, width]``, so that a (page, tensor, head) block of page_size * width elements is
+contiguous; for keys and values that is ``[num_pages, 2, kv_heads, page_size, head_dim]``, which the
+attention kernels read.  The
 reference keeps ``[2, num_blocks, block_size, kv_heads, head_dim]`` per layer
 (backends/vllm/src/worker.rs:592-595, models/src/flash_attention.rs:239-246); the
 layout is private to the cache and the kernels.  The number of pages follows the
@@ -22,13 +24,23 @@ from .spec import CacheGroup, LayerCache
 def page_bytes(group: CacheGroup, page_size: int, dtype: torch.dtype) -> int:
     """Bytes one page id costs in its group, all layers of the group together."""
     elem = torch.empty((), dtype=dtype).element_size()
-    return 2 * group.need.num_kv_heads * page_size * group.need.head_dim * elem * len(group.layers)
+    return group.need.elements_per_token * page_size * elem * len(group.layers)
 
 
-def pages_for_memory(groups: List[CacheGroup], page_size: int, dtype: torch.dtype, budget_bytes: int) -> int:
-    """Pages per pool (the same for every pool) that fit the budget."""
+def state_bytes_total(model, max_seqs: int) -> int:
+    """Bytes of the fixed-size per-request state of all layer runs, for ``max_seqs`` slots."""
+    return max_seqs * sum(int(n) for n in model.state_bytes)
+
+
+def pages_for_memory(groups: List[CacheGroup], page_size: int, dtype: torch.dtype, free_bytes: int,
+                     gpu_memory_utilization: float, state_bytes: int = 0, workspace_bytes: int = 0):
+    """Pages per pool (the same for every pool) from the memory that is free once the weights are loaded:
+    floor(free * utilization) / bytes per page over all layers, the reference's arithmetic
+    (backends/vllm/src/config.rs:626-641, 708-718), after the state slots and the step's working memory
+    have been taken out of the budget.  Returns (pages, budget in bytes)."""
     per = sum(page_bytes(g, page_size, dtype) for g in groups)
-    return max(0, budget_bytes // per) if per else 0
+    budget = int(free_bytes * gpu_memory_utilization) - int(state_bytes) - int(workspace_bytes)
+    return (max(0, budget // per) if per else 0), budget
 
 
 class KVCache:
@@ -37,7 +49,7 @@ class KVCache:
         self.model, self.groups, self.page_size, self.rt = model, groups, page_size, rt
         self.pages: List[torch.Tensor] = []
         for g in groups:
-            shape = (len(g.layers), g.num_pages, 2, g.need.num_kv_heads, page_size, g.need.head_dim)
+            shape = (len(g.layers), g.num_pages, g.need.elements_per_token * page_size)
             t = torch.empty(shape, dtype=rt.dtype, device=rt.device)
             # Poison: a key or value that is read without having been written shows as NaN.
             t.fill_(float("nan")) if poison else t.zero_()
@@ -54,8 +66,15 @@ class KVCache:
         if where is None:
             return LayerCache(group=-1, page_size=self.page_size, writes=False, state=state)
         gi, idx = where
-        return LayerCache(group=gi, pages=self.pages[gi][idx], num_pages=self.groups[gi].num_pages,
-                          page_size=self.page_size, writes=writes, state=state)
+        need, flat, ps = self.groups[gi].need, self.pages[gi][idx], self.page_size
+        named, at = {}, 0
+        for t in need.tensors:
+            n = t.heads * ps * t.width
+            named[t.name] = flat[:, at:at + n].unflatten(1, (t.heads, ps, t.width))
+            at += n
+        pages = flat.view(flat.shape[0], 2, need.num_kv_heads, ps, need.head_dim) if need.is_kv else flat
+        return LayerCache(group=gi, pages=pages, num_pages=self.groups[gi].num_pages, page_size=ps, writes=writes,
+                          state=state, tensors=named)
 
     def reset_state(self, slot: int) -> None:
         for t in self.state.values():

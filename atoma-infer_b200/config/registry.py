@@ -4,7 +4,8 @@ The reference picks its model at compile time (a cargo feature and a generic
 parameter, server/src/main.rs:45, backends/src/lib.rs:10-13).  Here the name in
 ``config.json``'s ``architectures[0]`` (or, failing that, its ``model_type``) picks an ``Architecture`` at run time, and
 each layer of the model spec an architecture returns names its parts by kind
-("attention", "swiglu", "rmsnorm", "rope", "prenorm"), which these tables resolve.
+("attention", "swiglu", "rmsnorm", "rope", "prenorm"; the model's two ends: "token", "linear"), which these
+tables resolve.
 Another architecture or another part is added by one ``register_*`` call from any
 module; nothing in the engine names a model.
 """
@@ -29,7 +30,7 @@ class Architecture:
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 _PARTS: Dict[str, Dict[str, type]] = {
-    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {},
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {},
 }
 
 
@@ -79,7 +80,7 @@ def architecture_of(model_dir: str):
 
 
 def register_part(family: str, kind: str, cls: type, *, replace: bool = False) -> None:
-    """family: 'mixer' | 'feed_forward' | 'norm' | 'position' | 'block'."""
+    """family: 'mixer' | 'feed_forward' | 'norm' | 'position' | 'block' | 'embedding' | 'head'."""
     if family not in _PARTS:
         raise ConfigError(f"unknown part family {family!r} (known: {sorted(_PARTS)})")
     if kind in _PARTS[family] and not replace:

@@ -140,5 +140,5 @@ def all_kernel_libraries():
 
     return [("core", CORE_SOURCES, None), ("gemm_tcgen05", GEMM_SOURCES, None)] + [
         (f"attention_d{d}", ATTENTION_SOURCES, {"HEAD_DIM": d}) for d in ATTENTION_HEAD_DIMS] + [
-        ("attention_noalloc_d64", ["kernels/attention_noalloc.cu"], {"HEAD_DIM": 64})] + [
+        (f"attention_noalloc_d{d}", ["kernels/attention_noalloc.cu"], {"HEAD_DIM": d}) for d in (64, 128)] + [
         (f"attention_tc_d{d}", ATTENTION_TC_SOURCES, {"HEAD_DIM": d}) for d in ATTENTION_TC_HEAD_DIMS]

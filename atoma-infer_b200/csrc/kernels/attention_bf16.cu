@@ -1170,9 +1170,10 @@ namespace {
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-int g_decode_tma = 1;
+int g_decode_tma = 0;
 }  // namespace
-// 0: the decode kernel loads pages with cp.async even where it could use TMA (for comparison).
+// 1: the decode kernel loads pages by TMA where it can (head size 64, pages of 8, 16 or 32 tokens, no window);
+// measured no faster than cp.async, so it is off unless asked for.
 extern "C" void attn_set_decode_tma(int on) { g_decode_tma = on; }
 
 extern "C" int attn_head_dim() { return D; }
@@ -1184,6 +1185,13 @@ extern "C" int attn_decode_max_cluster() { return DEC_MAX_CLUSTER; }
 // Float32 words of scratch that attn_decode needs for `splits` > 1: partial outputs and (max, sum) pairs.
 extern "C" size_t attn_decode_scratch_floats(int S, int nq, int splits) {
     return splits > 1 ? (size_t)S * nq * splits * (D + 2) : 0;
+}
+
+// The most splits the scratch-path merge takes: the block that merges stages a (max, sum) pair per (head of
+// the group, split) in the shared memory of its key tiles.
+extern "C" int attn_decode_max_splits(int nq, int nkv) {
+    const int G = nkv > 0 && nq >= nkv ? nq / nkv : 1;
+    return (int)(DEC_WARPS * DEC_WARP_ELEMS * sizeof(bf16) / ((size_t)G * 2 * sizeof(float)));
 }
 
 extern "C" int attn_prefill(const void* q, int q_stride, const void* cache, const int* meta, int group,
@@ -1274,17 +1282,22 @@ extern "C" int attn_decode(const void* q, int q_stride, const void* cache, const
     if (splits == 1) cluster_merge = 0;
     if (cluster_merge && splits > DEC_MAX_CLUSTER) return (int)cudaErrorInvalidValue;
     if (splits > 1 && !cluster_merge && (!scratch || !counters)) return (int)cudaErrorInvalidValue;
+    if (splits > 1 && !cluster_merge && splits > attn_decode_max_splits(nq, nkv)) return (int)cudaErrorInvalidValue;
     if (inv_freq && (rot % 2 || rot > D || rot <= 0)) return (int)cudaErrorInvalidValue;
     CacheLayout L{nkv, page_size, D};
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)S * nq * splits * D : nullptr;
     (void)max_context;
     const size_t smem = DEC_SMEM + 1024;  // room to start the tiles on a 1024-byte boundary
-    static bool configured = false;  // once: the attribute is not set again inside a stream capture
-    if (!configured) {
+    // Once per device: the attribute belongs to the device's copy of the kernel, and it is not set again
+    // inside a stream capture.
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0) return (int)cudaErrorInvalidDevice;
+    if (dev >= 64 || !configured[dev]) {
         cudaError_t err = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return (int)err;
-        configured = true;
+        if (dev < 64) configured[dev] = true;
     }
     // Page loads by TMA when a page's rows tile a warp's 32-key tile and start on its boundaries.
     CUtensorMap map;

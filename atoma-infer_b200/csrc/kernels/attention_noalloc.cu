@@ -33,6 +33,14 @@ extern "C" int attn_decode_noalloc(const void* q, int q_stride, const void* cach
     char msg[256];
     if (S <= 0 || nq <= 0 || nkv <= 0 || splits < 1 || page_size <= 0)
         return fail(ATTN_NOALLOC_BAD_ARGUMENT, err, err_cap, "attn_decode_noalloc: S, heads, splits and page_size must be positive");
+    if (nq % nkv || nq / nkv > 16)
+        return fail(ATTN_NOALLOC_BAD_ARGUMENT, err, err_cap,
+                    "attn_decode_noalloc: the query heads must be a multiple (at most 16 times) of the key/value heads");
+    if (splits > attn_decode_max_splits(nq, nkv)) {
+        snprintf(msg, sizeof msg, "attn_decode_noalloc: %d splits; with %d query heads per key/value head the merge takes "
+                 "at most %d", splits, nq / nkv, attn_decode_max_splits(nq, nkv));
+        return fail(ATTN_NOALLOC_TOO_LARGE, err, err_cap, msg);
+    }
     const size_t need = attn_decode_scratch_floats(S, nq, splits);
     if ((size_t)S * nkv > (size_t)ATTN_NOALLOC_MAX_GROUPS) {
         snprintf(msg, sizeof msg, "attn_decode_noalloc: %d requests x %d key/value heads exceed the %d built-in split counters",

@@ -16,10 +16,17 @@
 //  * Limit: S * num_q_heads * splits * (HEAD_DIM + 2) floats must not exceed
 //    ATTN_NOALLOC_SCRATCH_FLOATS (1 Mi floats = 4 MiB).  Larger calls are refused
 //    with ATTN_NOALLOC_TOO_LARGE and a message; nothing is launched.
+//    Also splits must not exceed attn_decode_max_splits(nq, nkv) (exported by the same
+//    library; 512 or more for head size 64, whatever the group size): the block that merges
+//    the splits stages their (max, sum) pairs in its shared memory.
 //  * Every GPU that loads this library holds the 4 MiB until the process exits.
+//  * Pages are loaded with cp.async, as in the engine (the library's opt-in TMA page
+//    loads, attn_set_decode_tma(1), apply to this entry point too).
 //  * The first call on a device looks up the array's device address (one
 //    cudaGetSymbolAddress) and sets the kernel's shared-memory attribute; make that
-//    first call outside any stream capture.  Later calls do neither.
+//    first call outside any stream capture.  Later calls do neither.  The first call
+//    on a device is not guarded against a second host thread making it at the same
+//    time: make it from one thread, then any thread may call.
 //  * It calls no cudaMalloc, cudaFree or any allocating routine, on any path.
 //    Also S * num_kv_heads must not exceed ATTN_NOALLOC_MAX_GROUPS (4096).
 //  * All calls share the one array and it keeps what the last call left.  The

@@ -16,12 +16,12 @@ int g_use_pdl = 1;
 extern "C" void kernels_set_pdl(int mode) { g_use_pdl = mode; }
 
 // ----------------------------------------------------------------------------- embedding
-// resid[t, :] = table[tokens[t], :], widened to float32 (the residual stream is float32).
+// resid[t, :] = scale * table[tokens[t], :], widened to float32 (the residual stream is float32).
 // A negative token id -1 - s stands for "the token last sampled into slot s" (last_tokens[s]):
 // a decode step can be launched before the host has read the previous step's tokens.
 template <typename T>
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
-                                  float* __restrict__ resid, const int* __restrict__ meta, int H, int V,
+                                  float* __restrict__ resid, const int* __restrict__ meta, int H, int V, float scale,
                                   const int* __restrict__ last_tokens, int num_slots, int* __restrict__ status) {
     pdl_launch_dependents();
     pdl_wait();
@@ -34,18 +34,19 @@ __global__ void embed_rows_kernel(const int* __restrict__ tokens, const T* __res
     if (bad && threadIdx.x == 0) atomicExch(&status[STATUS_BAD_TOKEN], 1 + t);
     const T* row = table + (size_t)(bad ? 0 : tok) * H;
     float* out = resid + (size_t)t * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = bad ? 0.f : to_float(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = bad ? 0.f : scale * to_float(row[i]);
 }
 
 extern "C" int embed_rows(const int* tokens, const void* table, int table_dtype, float* resid, const int* meta,
-                          int T, int H, int V, const int* last_tokens, int num_slots, int* status, cudaStream_t stream) {
+                          int T, int H, int V, float scale, const int* last_tokens, int num_slots, int* status,
+                          cudaStream_t stream) {
     if (T <= 0) return 0;
     int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == DT_F32)
-        return (int)launch_kernel(embed_rows_kernel<float>, T, threads, 0, stream, tokens, (const float*)table, resid, meta, H, V, last_tokens,
-                                  num_slots, status);
+        return (int)launch_kernel(embed_rows_kernel<float>, T, threads, 0, stream, tokens, (const float*)table, resid, meta, H, V, scale,
+                                  last_tokens, num_slots, status);
     return (int)launch_kernel(embed_rows_kernel<__nv_bfloat16>, T, threads, 0, stream, tokens, (const __nv_bfloat16*)table, resid,
-                              meta, H, V, last_tokens, num_slots, status);
+                              meta, H, V, scale, last_tokens, num_slots, status);
 }
 
 // ----------------------------------------------------------------------------- RMSNorm

@@ -125,12 +125,13 @@ class CudaOps:
             raise KernelError("device status: " + what)
 
     # ------------------------------------------------------------------ kernels
-    def embed(self, tokens, table, resid, meta, T: int):
-        """A token id -1 - s means: the token last sampled into slot s (``self.last_tokens``)."""
+    def embed(self, tokens, table, resid, meta, T: int, scale: float = 1.0):
+        """resid[t] = scale * table[tokens[t]].  A token id -1 - s means: the token last sampled into slot s
+        (``self.last_tokens``)."""
         H, V = table.shape[1], table.shape[0]
         self._check(self.lib.embed_rows(_p(tokens), _p(table), _code(table), _p(resid), _p(meta), T, H, V,
-                                        _p(self.last_tokens), self.last_tokens.numel(), _p(self.status), self._stream()),
-                    "embed_rows")
+                                        ctypes.c_float(scale), _p(self.last_tokens), self.last_tokens.numel(),
+                                        _p(self.status), self._stream()), "embed_rows")
 
     def add_rmsnorm(self, resid, delta, w, eps: float, out, meta, n: int, rows=None):
         """resid += delta (if given); out = rmsnorm(resid) * w.  With ``rows`` the sum and the

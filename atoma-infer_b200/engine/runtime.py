@@ -13,7 +13,7 @@ from typing import Optional
 
 import torch
 
-from ..cache.kv_cache import KVCache, pages_for_memory
+from ..cache.kv_cache import KVCache, pages_for_memory, state_bytes_total
 from ..cache.manager import CacheManager
 from ..config.engine_config import canonical_dtype
 from ..config.registry import architecture_of
@@ -36,6 +36,7 @@ class LoadedModel:
     step: StepFunction
     page_size: int
     num_pages: int  # usable pages per pool
+    memory: Optional[dict] = None  # how the pools were sized from free memory (None: a page count was given)
 
 
 def make_runtime(dtype: str, device=None, ops=None) -> Runtime:
@@ -48,11 +49,24 @@ def make_runtime(dtype: str, device=None, ops=None) -> Runtime:
     return Runtime(device=device, dtype=tdtype, ops=ops if ops is not None else CudaOps(device))
 
 
+def step_workspace_bytes(model: DecoderModel, dtype: torch.dtype, max_batched_tokens: int, max_seqs: int) -> int:
+    """An upper estimate of what a step allocates besides the cache: per token the float32 residual stream and
+    some ten rows of the widest activation any part says it makes (intermediate results live one or two at a
+    time), and the float32 logits of one row per request; twice over, because captured decode graphs keep a
+    pool of their own."""
+    elem = torch.empty((), dtype=dtype).element_size()
+    spec = model.spec
+    widest = max([spec.hidden_size] + [blk.activation_width() for blk in model.blocks])
+    per_token = 4 * spec.hidden_size + 10 * widest * elem
+    return 2 * (max_batched_tokens * per_token + max(max_seqs, 1) * spec.vocab_size * 4)
+
+
 def load_model(model_dir: str, *, dtype: str = "bfloat16", device=None, page_size: int = 16,
                num_pages: Optional[int] = None, max_seqs: int = 64, gpu_memory_utilization: float = 0.9,
                poison_cache: bool = False, ops=None, cuda_graphs: bool = False,
-               max_model_len: Optional[int] = None) -> LoadedModel:
-    """``num_pages``: usable pages per pool; None sizes the pools from free device memory."""
+               max_model_len: Optional[int] = None, max_batched_tokens: int = 2048) -> LoadedModel:
+    """``num_pages``: usable pages per pool; None sizes the pools from free device memory, leaving room for
+    the state slots of ``max_seqs`` requests and for the working memory of a step of ``max_batched_tokens``."""
     arch, config = architecture_of(model_dir)
     spec = arch.build_spec(config)
     model = DecoderModel(spec)
@@ -61,16 +75,21 @@ def load_model(model_dir: str, *, dtype: str = "bfloat16", device=None, page_siz
     model.bind(tensors, rt)
     del tensors
     groups = model.groups
+    memory = None
     if num_pages is None:
         free, total = torch.cuda.mem_get_info(rt.device)
-        budget = int(free - (1.0 - gpu_memory_utilization) * total)
-        num_pages = pages_for_memory(groups, page_size, rt.dtype, budget) - 1
+        state = state_bytes_total(model, max_seqs)
+        work = step_workspace_bytes(model, rt.dtype, max_batched_tokens, max_seqs)
+        pages, budget = pages_for_memory(groups, page_size, rt.dtype, free, gpu_memory_utilization, state, work)
+        num_pages = pages - 1  # page 0 of a pool is never handed out
+        memory = {"free": free, "total": total, "utilization": gpu_memory_utilization, "state_bytes": state,
+                  "workspace_bytes": work, "budget": budget, "pages": num_pages}
         if num_pages <= 0:
-            raise RuntimeError("no device memory is left for the cache after loading the weights")
+            raise RuntimeError(f"no device memory is left for the cache after loading the weights ({memory})")
     for g in groups:
         g.num_pages = num_pages + 1  # page 0 is never handed out
     manager = CacheManager(page_size, groups, max_seqs)
     cache = KVCache(model, groups, page_size, max_seqs, rt, poison=poison_cache)
     limit = min(max_model_len or spec.max_position or 1 << 30, num_pages * page_size)
     step = StepFunction(model, cache, manager, rt, cuda_graphs=cuda_graphs, max_model_len=limit)
-    return LoadedModel(config, model, rt, manager, cache, step, page_size, num_pages)
+    return LoadedModel(config, model, rt, manager, cache, step, page_size, num_pages, memory)

@@ -71,11 +71,14 @@ class StepFunction:
         self.page_size = manager.page_size
         self._pinned = torch.cuda.is_available()
         self.steps = 0
+        self.h2d_bytes = 0  # bytes of step metadata copied to the device so far
         # Decode steps (every request brings one token and wants its logits) replay a CUDA graph
         # captured per padded batch size; the reference has no graphs.
         self.cuda_graphs = cuda_graphs and torch.cuda.is_available() and getattr(model, "graph_safe", True)
         self.max_model_len = max_model_len
-        self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}
+        self._graphs: Dict[Tuple[int, int], "_DecodeGraph"] = {}  # insertion order = least recently used first
+        self._graph_meta: Dict[int, torch.Tensor] = {}  # metadata buffer of a bucket, shared by its graphs
+        self._graph_pool = None                          # one memory pool for the activations of all graphs
         self.graph_replays = 0
 
     # ------------------------------------------------------------------ metadata
@@ -154,6 +157,7 @@ class StepFunction:
         return host, lay, infos, R
 
     def context(self, dev: torch.Tensor, lay: MetaLayout, infos: List[EntryInfo]) -> StepContext:
+        """Views into the step's metadata on the device, for the parts."""
         v = lambda o, n: dev[o:o + n]  # noqa: E731
         return StepContext(
             rt=self.rt, T=lay.T, S=lay.S, meta=dev,
@@ -163,7 +167,7 @@ class StepFunction:
             max_tokens_per_entry=max((i.num_tokens for i in infos), default=0),
             max_context=max((i.context_len + i.num_tokens for i in infos), default=0),
             decode_only=all(i.num_tokens == 1 for i in infos),
-            page_size=self.page_size,
+            page_size=self.page_size, table_offsets=tuple(lay.tables), table_strides=tuple(lay.strides),
         )
 
     # ------------------------------------------------------------------ the step
@@ -176,6 +180,7 @@ class StepFunction:
             return self._run_graph(entries)
         host, lay, infos, R = self.prepare(entries)
         dev = host.to(self.rt.device, non_blocking=True)
+        self.h2d_bytes += host.numel() * 4
         for i in infos:
             if i.is_new:
                 self.cache.reset_state(i.state_slot)
@@ -188,9 +193,10 @@ class StepFunction:
 
     # ------------------------------------------------------------------ decode steps as CUDA graphs
     GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+    MAX_GRAPHS = 32  # captured (batch bucket, context bound) pairs kept; beyond that the least recently used goes
 
     def _graph_eligible(self, entries: Sequence[StepEntry]) -> bool:
-        if not self.cuda_graphs or len(entries) > self.GRAPH_BUCKETS[-1] or self.cache.state:
+        if not self.cuda_graphs or len(entries) > self.GRAPH_BUCKETS[-1]:
             return False
         return all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
 
@@ -202,15 +208,25 @@ class StepFunction:
         longest = max((self.manager.num_tokens(e.req) if self.manager.has_request(e.req) else 0) for e in entries) + 1
         ctx_bound = max(256, 1 << (longest - 1).bit_length())
         key = (bucket, ctx_bound)
-        g = self._graphs.get(key)
+        g = self._graphs.pop(key, None)
         if g is None:
             cap_stride = -(-max(self.max_model_len, 1) // self.page_size)
-            cap = MetaLayout(bucket, bucket, bucket, (cap_stride,) * len(self.manager.groups)).size
-            g = self._graphs[key] = _DecodeGraph(torch.zeros(cap, dtype=torch.int32, device=self.rt.device), cap_stride)
+            meta = self._graph_meta.get(bucket)
+            if meta is None:
+                cap = MetaLayout(bucket, bucket, bucket, (cap_stride,) * len(self.manager.groups)).size
+                meta = self._graph_meta[bucket] = torch.zeros(cap, dtype=torch.int32, device=self.rt.device)
+            g = _DecodeGraph(meta, cap_stride)
+            while len(self._graphs) >= self.MAX_GRAPHS:  # the graph unused for longest goes
+                self._graphs.pop(next(iter(self._graphs)))
+        self._graphs[key] = g  # most recently used last
         host, lay, infos, R = self.prepare(entries, pad_to=bucket)
         if max(lay.strides, default=0) > g.cap_stride:
             raise RuntimeError(f"a request holds more pages than max_model_len ({self.max_model_len}) allows")
         g.meta[:lay.size].copy_(host, non_blocking=True)
+        self.h2d_bytes += host.numel() * 4
+        for i in infos:
+            if i.is_new:  # a one-token prompt is a decode step too: its state starts from zero
+                self.cache.reset_state(i.state_slot)
         if g.graph is None:
             ctx = self.context(g.meta, lay, [])
             # sizes that pick kernels and splits are those of the bucket, not of this batch
@@ -223,7 +239,11 @@ class StepFunction:
                 torch.cuda.synchronize(self.rt.device)
                 graph = torch.cuda.CUDAGraph()
                 before = self.rt.ops.launches
-                with torch.cuda.graph(graph):
+                if self._graph_pool is None:
+                    self._graph_pool = torch.cuda.graph_pool_handle()
+                # one pool for all graphs: only one replays at a time and its logits are consumed (sampled or
+                # copied) on the same stream before the next replay, so their activations may share memory
+                with torch.cuda.graph(graph, pool=self._graph_pool):
                     g.logits = self.model.forward(ctx, self.cache, rows, bucket)
                 g.kernels = self.rt.ops.launches - before  # own kernels in one replay
                 g.graph = graph

@@ -50,8 +50,11 @@ class Attention(Mixer):
     def kv_size(self):
         return self.num_kv_heads * self.head_dim
 
+    def activation_width(self):
+        return self.q_size + 2 * self.kv_size
+
     def cache_need(self):
-        return CacheNeed(self.num_kv_heads, self.head_dim, self.window)
+        return CacheNeed.kv(self.num_kv_heads, self.head_dim, self.window)
 
     def declare(self):
         pre = self.prefix

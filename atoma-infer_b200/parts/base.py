@@ -67,6 +67,15 @@ class StepContext:
     max_context: int = 0         # longest context_len + num_tokens in the batch
     decode_only: bool = False    # every entry brings exactly one token
     page_size: int = 0
+    table_offsets: Sequence[int] = ()   # per cache group: where its block tables start in ``meta`` ...
+    table_strides: Sequence[int] = ()   # ... and how long a request's row is
+
+    def block_table(self, group: int) -> torch.Tensor:
+        """The block tables of a cache group as a device view [S, pages per request]: entry k's row lists its
+        page ids by absolute page index (-1: no page).  For parts written with tensor operations; the
+        kernels read the same memory through ``meta``."""
+        off, stride = self.table_offsets[group], self.table_strides[group]
+        return self.meta[off:off + self.S * stride].view(self.S, stride)
 
 
 class Part:
@@ -81,6 +90,42 @@ class Part:
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
+
+    def activation_width(self) -> int:
+        """Elements per token of the widest intermediate result the part makes (0: nothing wider than the
+        model's width); the engine sizes its working memory from it when it sizes the cache."""
+        return 0
+
+
+class Embedding(Part):
+    """The first stage: the step's token ids (and whatever else of the step's metadata it wants, positions
+    for instance) become the float32 residual stream.  ``graph_safe = True`` on a subclass says that its
+    ``forward`` reads the step's metadata on the device only, so a decode step may be captured in a graph."""
+
+    graph_safe = False
+
+    def forward(self, ctx: StepContext) -> torch.Tensor:
+        """Returns the residual stream, float32 [ctx.T, hidden]."""
+        raise NotImplementedError
+
+    def table(self) -> Optional[torch.Tensor]:
+        """The [vocab, hidden] matrix, for a head that is tied to it (None: there is no such matrix)."""
+        return None
+
+
+class Head(Part):
+    """The last stage: normed rows become float32 logits over the vocabulary (``graph_safe`` as for the
+    embedding)."""
+
+    graph_safe = False
+
+    def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime, embedding: Optional["Embedding"] = None) -> None:
+        """``embedding``: the model's first stage, for a head that shares its matrix."""
+        self.rt = rt
+
+    def forward(self, h: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        """``h`` [rows, hidden] in the compute dtype; returns float32 [rows, vocab]."""
+        raise NotImplementedError
 
 
 class Norm(Part):

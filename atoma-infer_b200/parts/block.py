@@ -27,6 +27,9 @@ class PreNormBlock(Block):
     def parts(self):
         return [self.norm1, self.mixer, self.norm2, self.feed_forward]
 
+    def activation_width(self):
+        return max(p.activation_width() for p in self.parts())
+
     def declare(self):
         return [d for p in self.parts() for d in p.declare()]
 

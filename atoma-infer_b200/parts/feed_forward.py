@@ -19,6 +19,9 @@ class SwiGLU(FeedForward):
         self.hidden = int(params["hidden"])
         self.intermediate = int(params["intermediate"])
 
+    def activation_width(self):
+        return 2 * self.intermediate
+
     def declare(self):
         pre = self.prefix
         return [

@@ -5,7 +5,7 @@ per layer the kinds and parameters of block, mixer, feed-forward and norm, and a
 ``schedule`` — the list of layer runs.  A run names the layer to execute and the
 layer whose cache it uses, so a layer may run twice or read another layer's keys
 and values.  ``DecoderModel`` turns the spec into bound parts and runs a step:
-embedding, the scheduled blocks, the final norm at the wanted rows, the output head
+the embedding part, the scheduled blocks, the final norm at the wanted rows, the head part
 (models/src/llama.rs:456-478 has this sequence fixed for one model).
 """
 from __future__ import annotations
@@ -21,7 +21,7 @@ from ..weights.loader import TensorDecl
 from .base import LayerCache, Runtime, StepContext
 
 # the registrations of the built-in parts
-from . import attention, block, feed_forward, norm, position  # noqa: F401
+from . import attention, block, embedding, feed_forward, head, norm, position  # noqa: F401
 
 
 @dataclass
@@ -45,6 +45,10 @@ class ModelSpec:
     embedding_tensor: str = "model.embed_tokens.weight"
     final_norm_prefix: str = "model.norm"
     head_tensor: Optional[str] = "lm_head.weight"   # None: the embedding matrix is the head
+    # The two ends of the model as parts, by kind like the rest.  None: the plain ones, a token table named
+    # ``embedding_tensor`` and a bias-free linear head on ``head_tensor``.
+    embedding: Optional[Dict[str, Any]] = None
+    head: Optional[Dict[str, Any]] = None
     schedule: Optional[List[LayerRun]] = None       # None: every layer once, in order
     ignored_tensors: Tuple[str, ...] = ()           # globs a checkpoint may carry unused
     max_position: int = 0
@@ -53,20 +57,32 @@ class ModelSpec:
     def runs(self) -> List[LayerRun]:
         return self.schedule if self.schedule is not None else [LayerRun(i) for i in range(len(self.layers))]
 
+    def embedding_spec(self) -> Dict[str, Any]:
+        return self.embedding or {"kind": "token", "vocab": self.vocab_size, "hidden": self.hidden_size,
+                                  "tensor": self.embedding_tensor}
+
+    def head_spec(self) -> Dict[str, Any]:
+        return self.head or {"kind": "linear", "vocab": self.vocab_size, "hidden": self.hidden_size,
+                             "tensor": self.head_tensor}
+
 
 def _build_layers(spec: ModelSpec):
     return [part_class("block", ls.block["kind"])(ls.block, ls.prefix) for ls in spec.layers]
 
 
+def _build_ends(spec: ModelSpec):
+    e, h = spec.embedding_spec(), spec.head_spec()
+    return part_class("embedding", e["kind"])(e, ""), part_class("head", h["kind"])(h, "")
+
+
 def declared_tensors(spec: ModelSpec) -> List[TensorDecl]:
     """Every checkpoint tensor the model needs, by name and shape."""
-    decls = [TensorDecl(spec.embedding_tensor, (spec.vocab_size, spec.hidden_size))]
+    embedding, head = _build_ends(spec)
+    decls = embedding.declare()
     for blk in _build_layers(spec):
         decls += blk.declare()
     decls += part_class("norm", spec.final_norm["kind"])(spec.final_norm, spec.final_norm_prefix).declare()
-    if spec.head_tensor:
-        decls.append(TensorDecl(spec.head_tensor, (spec.vocab_size, spec.hidden_size)))
-    return decls
+    return decls + head.declare()
 
 
 class DecoderModel:
@@ -75,6 +91,7 @@ class DecoderModel:
     def __init__(self, spec: ModelSpec):
         self.spec = spec
         self.blocks = _build_layers(spec)
+        self.embedding, self.head = _build_ends(spec)
         self.final_norm = part_class("norm", spec.final_norm["kind"])(spec.final_norm, spec.final_norm_prefix)
         self.runs = spec.runs()
         # Who owns which cache: a run without ``cache_of`` owns pages (and state) of its own, so a layer
@@ -114,26 +131,28 @@ class DecoderModel:
         # fixed-size state per request, for every run of a mixer that has some
         self.state_bytes = [self.blocks[r.layer].mixer.state_bytes() for r in self.runs]
         # a step of this model can be captured in a CUDA graph if no part reads the host-side entry list
-        self.graph_safe = all(getattr(blk.mixer, "graph_safe", False) for blk in self.blocks)
+        self.graph_safe = all(getattr(p, "graph_safe", False)
+                              for p in [self.embedding, self.head] + [blk.mixer for blk in self.blocks])
 
     def declare(self) -> List[TensorDecl]:
-        return declared_tensors(self.spec)
+        decls = self.embedding.declare()
+        for blk in self.blocks:
+            decls += blk.declare()
+        return decls + self.final_norm.declare() + self.head.declare()
 
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
-        self.embedding = tensors[self.spec.embedding_tensor]
-        self.head = tensors[self.spec.head_tensor] if self.spec.head_tensor else self.embedding
+        self.embedding.bind(tensors, rt)
         for blk in self.blocks:
             blk.bind(tensors, rt)
         self.final_norm.bind(tensors, rt)
+        self.head.bind(tensors, rt, self.embedding)
 
     # ------------------------------------------------------------------ the forward pass of one step
     def forward(self, ctx: StepContext, cache, rows: torch.Tensor, num_rows: int) -> torch.Tensor:
         """Runs the step's tokens through the model; returns float32 logits [num_rows, vocab]
         at the flat-batch rows listed in ``rows`` (a device int32 array)."""
-        ops = self.rt.ops
-        resid = torch.empty((ctx.T, self.spec.hidden_size), dtype=torch.float32, device=self.rt.device)
-        ops.embed(ctx.tokens, self.embedding, resid, ctx.meta, ctx.T)
+        resid = self.embedding.forward(ctx)
         delta = None
         for i, run in enumerate(self.runs):
             view = cache.layer_view(self.run_owner[i], writes=run.cache_of is None, state_run=i)
@@ -141,4 +160,4 @@ class DecoderModel:
         if num_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
         h = self.final_norm.forward(resid, delta, ctx, rows=rows, num_rows=num_rows)
-        return ops.linear(h, self.head, out_dtype=torch.float32, meta=ctx.meta, use_rows=True)
+        return self.head.forward(h, ctx)

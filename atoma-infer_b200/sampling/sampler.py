@@ -20,6 +20,7 @@ class Sampler:
     def __init__(self, rt):
         self.rt = rt
         self._pinned = torch.cuda.is_available()
+        self.h2d_bytes = self.d2h_bytes = 0  # bytes copied to and from the device so far
 
     def sample(self, logits: torch.Tensor, params: Sequence[ResolvedParams], steps: Sequence[int],
                histories: Sequence[Sequence[int]], slots: Sequence[int] = (), defer: bool = False):
@@ -50,6 +51,7 @@ class Sampler:
         h[5 * R:6 * R] = [p.top_k for p in params]
         h[6 * R:7 * R].view(np.float32)[:] = [p.top_p for p in params]
         d = host.to(dev, non_blocking=True)
+        self.h2d_bytes += host.numel() * 4
         out = torch.empty(R, dtype=torch.int32, device=dev)
         ops.sample(logits, d[4 * R:5 * R].view(torch.float32), d[5 * R:6 * R], d[6 * R:7 * R].view(torch.float32),
                    d[0:2 * R], d[2 * R:4 * R], out, slots=d[7 * R:8 * R] if S else None)
@@ -58,6 +60,7 @@ class Sampler:
         status = getattr(ops, "status", None)
         ns = status.numel() if status is not None else 0
         back = torch.empty(R + ns, dtype=torch.int32, pin_memory=self._pinned)
+        self.d2h_bytes += back.numel() * 4
         back[:R].copy_(out, non_blocking=True)
         if ns:  # the status words ride along: the host sees a kernel's complaint with the tokens it spoilt
             back[R:].copy_(status, non_blocking=True)

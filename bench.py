@@ -32,7 +32,7 @@ MODEL = {  # Llama 3.2 1B
                      "original_max_position_embeddings": 8192, "rope_type": "llama3"},
     "max_position_embeddings": 131072, "tie_word_embeddings": True, "bos_token_id": 128000, "eos_token_id": 128001,
 }
-PROMPT_LEN, PREFILL_TOKENS, DECODE_TOKENS, PAGE = 2048, 2048, 256, 16
+PROMPT_LEN, PREFILL_TOKENS, PAGE = 2048, 2048, 16
 
 
 def peaks():
@@ -56,7 +56,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -127,7 +127,7 @@ def main() -> int:
     kv_bytes_per_token = 2 * L * nkv * d * 2
 
     max_batch = 64 if not args.skip_points else args.batch
-    tokens_per_req = PROMPT_LEN + DECODE_TOKENS + args.steps + args.warmup + 64
+    tokens_per_req = PROMPT_LEN + 5 * args.steps + args.warmup + 64
     pages = max_batch * (-(-tokens_per_req // PAGE)) + 256
     eng = Engine(tmp, dtype="bfloat16", block_size=PAGE, num_gpu_blocks_override=pages,
                  max_num_sequences=max(max_batch, 8), max_num_batched_tokens=max(PREFILL_TOKENS, max_batch))
@@ -162,73 +162,93 @@ def main() -> int:
                "frac": prefill_flops / (prefill_ms * 1e-3) / (bf16_tflops * 1e12), "peak": f"{peak_kind} bf16 burst"}
 
     # ------------------------------------------------------------------ decode
+    REPEATS = 5
+
     def decode_run(batch, steps, warmup, through_engine):
-        """Prefills ``batch`` requests, then times ``steps`` decode steps after ``warmup``."""
+        """Prefills ``batch`` requests, warms up, then times ``steps`` decode steps REPEATS times over (the
+        context grows from one repeat to the next).  Returns a record of the median repeat."""
         ids = [eng.add_request(prompt(), greedy) for _ in range(batch)]
         while any(eng.scheduler.num_computed(i) < PROMPT_LEN for i in ids):
             eng.step()  # prompts in portions under the token budget; the last portion samples
         for _ in range(warmup):
             eng.step()
-        launches0 = ops.launches
-        if through_engine:
-            ms = event_ms(lambda: [eng.step() for _ in range(steps)])
-        else:
-            # device-timed: the same decode step with the tokens already on the host side
-            # (synthetic ids), no read-back between steps
-            fake = torch.randint(0, V, (steps, batch), generator=g).tolist()
-            out = torch.empty(batch, dtype=torch.int32, device=lm.rt.device)
+        runs = []
+        for rep in range(REPEATS):
+            launches0 = ops.launches
+            h2d0, d2h0 = lm.step.h2d_bytes + eng.sampler.h2d_bytes, eng.sampler.d2h_bytes
+            ctx0 = lm.manager.num_tokens(ids[0])  # tokens in the cache when the region starts
+            if through_engine:
+                ms = event_ms(lambda: [eng.step() for _ in range(steps)])
+            else:
+                # device-timed: the same decode step with the tokens already on the host side
+                # (synthetic ids), no read-back between steps
+                fake = torch.randint(0, V, (steps, batch), generator=g).tolist()
+                out = torch.empty(batch, dtype=torch.int32, device=lm.rt.device)
 
-            def loop():
-                for s in range(steps):
-                    logits = lm.step.run([StepEntry(i, [fake[s][k]], [0]) for k, i in enumerate(ids)])
-                    ops.sample(logits, None, None, None, None, None, out)
-            ms = event_ms(loop)
-        launches = ops.launches - launches0
-        ctx_mid = PROMPT_LEN + warmup + steps / 2
+                def loop():
+                    for s in range(steps):
+                        logits = lm.step.run([StepEntry(i, [fake[s][k]], [0]) for k, i in enumerate(ids)])
+                        ops.sample(logits, None, None, None, None, None, out)
+                ms = event_ms(loop)
+            ctx_mid = ctx0 + steps / 2
+            nbytes = weight_bytes + batch * ctx_mid * kv_bytes_per_token
+            runs.append({"ms": ms, "launches": ops.launches - launches0, "ctx_mid": ctx_mid, "bytes": nbytes,
+                         "h2d": (lm.step.h2d_bytes + eng.sampler.h2d_bytes - h2d0) / steps,
+                         "d2h": (eng.sampler.d2h_bytes - d2h0) / steps})
         for i in ids:
             eng.abort_request(i)
-        return ms, launches, ctx_mid
+        runs.sort(key=lambda r: r["ms"])
+        med = dict(runs[len(runs) // 2])
+        med["ms_min"], med["ms_max"] = runs[0]["ms"], runs[-1]["ms"]
+        return med
+
+    def roofline_of(run, batch, steps):
+        ms_step = run["ms"] / steps
+        achieved = run["bytes"] / (ms_step * 1e-3) / 1e9
+        return {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs,
+                "of": peak_kind, "ms_per_step": ms_step, "ms_per_step_min": run["ms_min"] / steps,
+                "ms_per_step_max": run["ms_max"] / steps, "bytes": run["bytes"], "context": run["ctx_mid"],
+                "tok_s": batch * steps / run["ms"] * 1e3}
 
     if args.phase == "prefill":
         print(json.dumps({"impl": "ours", "phase": "prefill", "prefill": prefill}))
         return 0
     clocks = ClockSampler()
     clocks.start()
-    ms, launches, ctx_mid = decode_run(args.batch, args.steps, args.warmup, through_engine=False)
-    clock_rec = clocks.stop()
-    ms_step = ms / args.steps
-    value = args.batch * args.steps / ms * 1e3
-    step_bytes = weight_bytes + args.batch * ctx_mid * kv_bytes_per_token
-    achieved = step_bytes / (ms_step * 1e-3) / 1e9
-    e2e_ms = float("nan")
+    run = decode_run(args.batch, args.steps, args.warmup, through_engine=False)
+    roofline = roofline_of(run, args.batch, args.steps)
+    e2e = None
     if args.phase == "all":
-        e2e_ms, _, _ = decode_run(args.batch, args.steps, args.warmup, through_engine=True)
-    meta_ints = 20 + 3 * args.batch + (args.batch + 1) + 2 * args.batch + args.batch \
-        + args.batch * (-(-(PROMPT_LEN + DECODE_TOKENS) // PAGE))
-    points = {}
+        e2e = decode_run(args.batch, args.steps, args.warmup, through_engine=True)
+    points, points_roofline = {}, {f"decode_b{args.batch}": roofline}
     if not args.skip_points and args.phase == "all":
         for b in (1, 64):
-            pms, _, _ = decode_run(b, 32, 3, through_engine=False)
-            points[f"decode_b{b}"] = b * 32 / pms * 1e3
+            r = roofline_of(decode_run(b, args.steps, args.warmup, through_engine=False), b, args.steps)
+            points[f"decode_b{b}"] = r["tok_s"]
+            points_roofline[f"decode_b{b}"] = r
+    clock_rec = clocks.stop()
 
     rec = {
-        "metric": "decode tok/s (Llama 3.2 1B, batch 8, 2,048-token prompts)", "value": value, "unit": "tok/s",
-        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "metric": "decode tok/s (Llama 3.2 1B, batch 8, 2,048-token prompts)", "value": roofline["tok_s"], "unit": "tok/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": roofline["ms_per_step"],
+        "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
         "config": {
             "model": "Llama-3.2-1B (random weights N(0,0.02), seed 0)", "layers": L,
             "layers_full": MODEL["num_hidden_layers"], "hidden": H, "heads": nq, "kv_heads": nkv, "head_dim": d,
             "intermediate": I, "vocab": V, "global_batch": args.batch, "seq_len": PROMPT_LEN, "context": 4096,
-            "decode_tokens": DECODE_TOKENS, "page_size": PAGE, "parallelism": "1 GPU",
+            "page_size": PAGE, "parallelism": "1 GPU", "repeats": f"median of {REPEATS} regions of --steps steps each",
             "l2": "inputs larger than L2 (2.47 GB of weights read every step)", "prompt_ids": "uniform, seed 2",
         },
-        "e2e": {"value": args.batch * args.steps / e2e_ms * 1e3, "unit": "tok/s",
-                "h2d_bytes_per_step": 4 * meta_ints + 28 * args.batch, "d2h_bytes_per_step": 4 * args.batch},
-        "gpu_launches": launches,
+        "e2e": None if e2e is None else {
+            "value": args.batch * args.steps / e2e["ms"] * 1e3, "unit": "tok/s",
+            "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+            "bytes_counted": "from the pinned buffers copied each step (metadata, sampler parameters; tokens back)"},
+        "gpu_launches": run["launches"],
         "prefill": prefill,
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s",
-                     "frac": achieved / hbm_gbs, "of": peak_kind},
+        "roofline": {k: roofline[k] for k in ("bound", "achieved", "peak", "unit", "frac", "of")},
         "points": points,
+        "points_roofline": points_roofline,
         "clocks": clock_rec,
     }
     print(json.dumps(rec))

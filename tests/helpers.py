@@ -209,3 +209,43 @@ def compare_trace(steps, out_dir: str, vocab: int, ref_logits: Dict[str, torch.T
                 r += 1
             pos[e["id"]] = start + len(e["tokens"])
     return worst, where, agree / max(total, 1)
+
+
+def greedy_agreement(w, cfg, prompt, got: Sequence[int], bound: float = 2 * BF16_TOL):
+    """Policy for greedy tokens of a reduced-precision engine.  Every generated token is judged against the
+    plain implementation run on the engine's own history (the prompt and the tokens generated before it), so
+    no token is lost to an earlier, permitted difference: it must be the plain top-1, or its plain logit must
+    lie within ``bound`` times the largest |logit| of that position below the top-1 (twice the tolerance the
+    logits themselves are held to, since both candidates may move).  Returns (tokens equal to the plain
+    top-1, tokens generated)."""
+    import plain_llama as P
+
+    logits = P.forward(w, cfg, list(prompt) + list(got))
+    same = 0
+    for i, tok in enumerate(got):
+        row = logits[len(prompt) - 1 + i]
+        best = int(torch.argmax(row))
+        if tok == best:
+            same += 1
+            continue
+        lead = float(row[best] - row[tok]) / float(row.abs().max())
+        assert lead <= bound, (f"token {i}: engine {tok}, plain {best}, although the plain top-1 leads it by "
+                               f"{lead:.3g} of the logit scale (bound {bound:.3g})")
+    return same, len(got)
+
+
+def plain_sampled(w, cfg, prompt, n, sp):
+    """The plain loop: whole sequence each time, penalty over the last ids, then the seeded draw."""
+    import plain_llama as P
+
+    p = sp.validated()
+    toks, out = list(prompt), []
+    for step in range(n):
+        logits = P.forward(w, cfg, toks)[-1]
+        if p.repetition_penalty != 1.0:
+            logits = P.apply_repeat_penalty(logits, p.repetition_penalty, toks[-p.repeat_last_n:])
+        t = P.greedy(logits) if p.greedy else P.sample(logits, temperature=p.temperature, seed=p.seed, step=step,
+                                                       top_k=p.top_k, top_p=p.top_p)
+        out.append(t)
+        toks.append(t)
+    return out

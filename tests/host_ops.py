@@ -43,13 +43,13 @@ class HostOps:
     def fast_attention(self, *a):
         return False
 
-    def embed(self, tokens, table, resid, meta, T):
+    def embed(self, tokens, table, resid, meta, T, scale=1.0):
         self._count()
         n = int(meta[META_NUM_TOKENS])
         tok = tokens[:n].long()
         neg = tok < 0
         tok = torch.where(neg, self.last_tokens[(-tok - 1).clamp(min=0)].long(), tok)
-        resid[:n] = table[tok].float()
+        resid[:n] = scale * table[tok].float()
 
     def add_rmsnorm(self, resid, delta, w, eps, out, meta, n, rows=None):
         self._count()

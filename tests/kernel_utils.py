@@ -7,6 +7,7 @@ import numpy as np
 import torch
 
 from atoma_infer_b200.csrc import ops as O
+from atoma_infer_b200.engine.step import MetaLayout
 from atoma_infer_b200.parts.base import EntryInfo, Runtime, StepContext
 
 
@@ -16,13 +17,10 @@ def make_context(rt: Runtime, entries: Sequence[Tuple[int, int]], page_size: int
     absolute page index).  Returns the context and the device array of wanted rows."""
     S, T, R = len(entries), sum(n for _, n in entries), len(rows)
     stride = max(len(t) for t in tables)
-    o = O.META_HEADER_INTS
-    off = {}
-    for name, n in (("tokens", T), ("positions", T), ("token_entry", T), ("cu", S + 1), ("ctx", S), ("slots", S),
-                    ("rows", max(R, 1)), ("tables", S * stride)):
-        off[name] = o
-        o += n
-    h = np.zeros(o, dtype=np.int32)
+    lay = MetaLayout(T, S, R, (stride,))  # the engine's own layout: a change of it reaches these tests too
+    off = {"tokens": lay.tokens, "positions": lay.positions, "token_entry": lay.token_entry, "cu": lay.cu,
+           "ctx": lay.ctx, "slots": lay.slots, "rows": lay.rows, "tables": lay.tables[0]}
+    h = np.zeros(lay.size, dtype=np.int32)
     h[O.META_NUM_TOKENS], h[O.META_NUM_ENTRIES], h[O.META_NUM_ROWS] = T, S, R
     h[O.META_BT_STRIDE], h[O.META_BT_OFFSET] = stride, off["tables"]
     infos, start = [], 0
@@ -46,7 +44,8 @@ def make_context(rt: Runtime, entries: Sequence[Tuple[int, int]], page_size: int
                       token_entry=v("token_entry", T), cu_tokens=v("cu", S + 1), context_lens=v("ctx", S),
                       state_slots=v("slots", S), entries=infos,
                       max_tokens_per_entry=max(n for _, n in entries), max_context=max(c + n for c, n in entries),
-                      decode_only=all(n == 1 for _, n in entries), page_size=page_size)
+                      decode_only=all(n == 1 for _, n in entries), page_size=page_size,
+                      table_offsets=tuple(lay.tables), table_strides=(stride,))
     return ctx, v("rows", max(R, 1))
 
 

@@ -7,7 +7,7 @@ from atoma_infer_b200.cache import CacheError, CacheGroup, CacheManager, CacheNe
 
 
 def mgr(pages=8, page_size=4, max_seqs=4, window=None, extra_groups=()):
-    groups = [CacheGroup(CacheNeed(2, 16, window), [0, 1], pages + 1)] + list(extra_groups)
+    groups = [CacheGroup(CacheNeed.kv(2, 16, window), [0, 1], pages + 1)] + list(extra_groups)
     return CacheManager(page_size, groups, max_seqs)
 
 
@@ -86,7 +86,7 @@ def test_window_group_gives_pages_back_as_the_window_passes():
 
 
 def test_groups_have_pools_of_their_own():
-    m = mgr(pages=8, window=None, extra_groups=[CacheGroup(CacheNeed(1, 32, 8), [2], 4)])
+    m = mgr(pages=8, window=None, extra_groups=[CacheGroup(CacheNeed.kv(1, 32, 8), [2], 4)])
     m.add_request(1)
     m.reserve(1, 12)
     assert len(m.table(1, 0)) == 3 and len(m.table(1, 1)) == 3

@@ -19,21 +19,6 @@ def _engine(d, page, **kw):
     return Engine(d, dtype="float32", block_size=page, cuda_graphs=False, ops=HostOps(), **kw)
 
 
-def _plain_sampled(w, cfg, prompt, n, sp):
-    """The plain loop: whole sequence each time, penalty over the last ids, then the seeded draw."""
-    p = sp.validated()
-    toks, out = list(prompt), []
-    for step in range(n):
-        logits = P.forward(w, cfg, toks)[-1]
-        if p.repetition_penalty != 1.0:
-            logits = P.apply_repeat_penalty(logits, p.repetition_penalty, toks[-p.repeat_last_n:])
-        t = P.greedy(logits) if p.greedy else P.sample(logits, temperature=p.temperature, seed=p.seed, step=step,
-                                                       top_k=p.top_k, top_p=p.top_p)
-        out.append(t)
-        toks.append(t)
-    return out
-
-
 def test_greedy_through_the_engine_with_few_pages(tiny_models):
     from atoma_infer_b200.sampling import SamplingParams
 
@@ -61,7 +46,7 @@ def test_sampling_options_reach_the_sampler(tiny_models):
            SamplingParams(temperature=0.7, top_k=9, top_p=0.8, random_seed=13, max_new_tokens=6, ignore_eos_token=True),
            SamplingParams(temperature=0.8, repetition_penalty=1.5, repeat_last_n=6, random_seed=14, max_new_tokens=6,
                           ignore_eos_token=True)]
-    want = [_plain_sampled(w, cfg, p, 6, sp) for p, sp in zip(prompts, sps)]
+    want = [helpers.plain_sampled(w, cfg, p, 6, sp) for p, sp in zip(prompts, sps)]
     got = [o.token_ids for o in _engine(d, page).generate(prompts, sps)]
     assert got == want
 

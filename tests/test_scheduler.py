@@ -8,7 +8,7 @@ from atoma_infer_b200.engine.scheduler import RUNNING, UNKNOWN, WAITING, Schedul
 
 
 def make(pages=8, budget=100, seqs=4, model_len=64, chunked=True, page_size=4):
-    cm = CacheManager(page_size, [CacheGroup(CacheNeed(1, 16), [0], pages + 1)], seqs)
+    cm = CacheManager(page_size, [CacheGroup(CacheNeed.kv(1, 16), [0], pages + 1)], seqs)
     return cm, Scheduler(cm, max_num_batched_tokens=budget, max_num_seqs=seqs, max_model_len=model_len,
                          enable_chunked_prefill=chunked)
 

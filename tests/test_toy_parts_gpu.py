@@ -11,6 +11,7 @@ import torch
 
 import helpers
 import plain_llama as P
+from toy_parts import RunningMeanMixer
 from atoma_infer_b200.config import register_architecture, register_part
 from atoma_infer_b200.parts import FeedForward, LayerRun, LayerSpec, Mixer, ModelSpec, PositionEncoding
 from atoma_infer_b200.weights import TensorDecl
@@ -18,40 +19,6 @@ from atoma_infer_b200.weights import TensorDecl
 pytestmark = pytest.mark.gpu
 
 H, V = 48, 97
-
-
-class RunningMeanMixer(Mixer):
-    """out[t] = W * mean(x[0..t]) over the request's tokens so far.  Its state (running sum and
-    count) is fixed-size per request and lives in the engine's state slots; it keeps no pages."""
-
-    graph_safe = False  # walks the host-side entry list
-
-    def __init__(self, params, prefix):
-        super().__init__(params, prefix)
-        self.hidden = int(params["hidden"])
-
-    def state_bytes(self):
-        return 4 * (self.hidden + 1)
-
-    def declare(self):
-        return [TensorDecl(self.prefix + ".mix.weight", (self.hidden, self.hidden))]
-
-    def bind(self, tensors, rt):
-        super().bind(tensors, rt)
-        self.w = tensors[self.prefix + ".mix.weight"].float()
-
-    def forward(self, x, ctx, cache):
-        out = torch.empty_like(x)
-        state = cache.state.view(torch.float32)  # [slots, hidden + 1]
-        for e in ctx.entries:
-            rows = slice(e.start, e.start + e.num_tokens)
-            s = state[e.state_slot]
-            sums = s[:self.hidden] + torch.cumsum(x[rows].float(), 0)
-            counts = s[self.hidden] + torch.arange(1, e.num_tokens + 1, device=x.device, dtype=torch.float32)
-            out[rows] = ((sums / counts[:, None]) @ self.w.T).to(x.dtype)
-            s[:self.hidden] = sums[-1]
-            s[self.hidden] = counts[-1]
-        return out
 
 
 def toy_config(raw):

@@ -46,11 +46,11 @@ def _case(rt, contexts, nq, nkv, d, page, seed):
     return ctx, cache, qkv, num_pages
 
 
-def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
+@pytest.mark.parametrize("nq,nkv,d,page,splits", [(8, 2, 64, 16, 4), (6, 2, 128, 8, 3)])
+def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row(nq, nkv, d, page, splits):
     from atoma_infer_b200.engine.runtime import make_runtime
 
     rt = make_runtime("bfloat16", "cuda:0")
-    nq, nkv, d, page, splits = 8, 2, 64, 16, 4
     lib = _library(d)
     err = ctypes.create_string_buffer(512)
     stream = ctypes.c_void_p(torch.cuda.current_stream(rt.device).cuda_stream)
@@ -81,3 +81,14 @@ def test_no_alloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
                                  ctx.cu_tokens.data_ptr(), ctx.positions.data_ptr(), got.data_ptr(), 2048, nq, nkv, page,
                                  num_pages, 0, scale, 32, ctx.max_context, rt.ops.status.data_ptr(), stream, err, 512)
     assert rc == -1 and b"floats of scratch" in err.value and b"1048576" in err.value
+    # more splits than the merging block can stage in its shared memory (the scratch array would hold them):
+    # refused as well, the message names the limit
+    most = lib.attn_decode_max_splits(16, 1)
+    rc = lib.attn_decode_noalloc(qkv.data_ptr(), qkv.shape[1], cache.data_ptr(), ctx.meta.data_ptr(), 0,
+                                 ctx.cu_tokens.data_ptr(), ctx.positions.data_ptr(), got.data_ptr(), 1, 16, 1, page,
+                                 num_pages, 0, scale, most + 1, ctx.max_context, rt.ops.status.data_ptr(), stream, err, 512)
+    assert rc == -1
+    if (most + 1) * 16 * (d + 2) <= (1 << 20):  # the case fits the array, so only the split limit refuses it
+        assert b"splits" in err.value and str(most).encode() in err.value
+    torch.cuda.synchronize()
+    rt.ops.check_status()
