@@ -177,12 +177,14 @@ def run_trace(model_dir: str, dtype: str, steps, out_dir: str, max_tokens: int, 
     return steps, out_dir
 
 
-def compare_trace(steps, out_dir: str, vocab: int, ref_logits: Dict[str, torch.Tensor], strip=1):
-    """Largest |difference| / largest |logit| over every wanted place, and the first place
-    where it exceeds nothing (for messages).  Request ids carry a ``strip``-letter tag."""
+def compare_trace(steps, out_dir: str, vocab: int, ref_logits: Dict[str, torch.Tensor], strip=1, bound=2 * BF16_TOL):
+    """Largest |difference| / largest |logit| over every wanted place, the place where it is reached (for
+    messages), the share of places whose top-1 equals the plain one, and that share among the places where the
+    plain top-1 leads the runner-up by more than ``bound`` times the logit scale (there a reduced-precision
+    engine has no excuse).  Request ids carry a ``strip``-letter tag."""
     pos: Dict[str, int] = {}
     worst, where = 0.0, None
-    agree = total = 0
+    agree = total = clear = clear_agree = 0
     for s in steps:
         wanted = sum(len(e["want"]) for e in s["entries"])
         if not wanted:
@@ -204,11 +206,16 @@ def compare_trace(steps, out_dir: str, vocab: int, ref_logits: Dict[str, torch.T
                     err = float("inf")
                 if err > worst:
                     worst, where = err, (s["step"], e["id"], start + w)
-                agree += int(got[r].argmax() == exp.argmax())
+                same = int(got[r].argmax() == exp.argmax())
+                agree += same
                 total += 1
+                top = np.partition(exp, -2)[-2:]
+                if vocab > 1 and float(top[1] - top[0]) > bound * scale:
+                    clear += 1
+                    clear_agree += same
                 r += 1
             pos[e["id"]] = start + len(e["tokens"])
-    return worst, where, agree / max(total, 1)
+    return worst, where, agree / max(total, 1), clear_agree / max(clear, 1)
 
 
 def greedy_agreement(w, cfg, prompt, got: Sequence[int], bound: float = 2 * BF16_TOL):

@@ -48,7 +48,7 @@ def test_llama_1b_layer_sizes(dtype, model, tmp_path):
         steps.append({"entries": e, "end": (["ma"] if i == 149 else []) + (["mb"] if i - 100 == len(b) - 1 else [])})
     steps, out = helpers.run_trace(d, dtype, steps, str(tmp_path), 320, 16, timeout=900)
     refs = dict(ref, a=ref["r0"], b=ref["r1"])  # ids "wr0", "wr1", "ma", "mb" lose their first letter
-    worst, where, agree = helpers.compare_trace(steps, out, CONFIG_1B_2L["vocab_size"], refs, strip=1)
+    worst, where, agree, clear = helpers.compare_trace(steps, out, CONFIG_1B_2L["vocab_size"], refs, strip=1)
     assert worst <= (5e-5 if dtype == "float32" else helpers.BF16_TOL), (worst, where)
     if dtype == "float32":
         assert agree == 1.0

@@ -7,6 +7,10 @@ import plain_llama as P
 
 pytestmark = pytest.mark.gpu
 
+# bfloat16 families: share of places whose top-1 token must equal the plain implementation's (random tiny models
+# have many near-ties, which is why it is not 1), and all of them where the plain lead is clear
+BF16_TOP1 = 0.9
+
 LENGTHS = {"A": (1, 7, 16, 33, 70, 131), "B": (5, 29, 64, 97, 150), "C": (3, 40, 129, 300)}
 
 
@@ -39,10 +43,12 @@ def test_every_cutting_matches_plain(name, dtype, tiny_models, references, tmp_p
     tol = helpers.FP32_TOL if dtype == "float32" else helpers.BF16_TOL
     for tag in families:
         sub = [s for s in steps if s["entries"][0]["id"].startswith(tag)]
-        worst, where, agree = helpers.compare_trace(sub, out, cfg["vocab_size"], ref)
+        worst, where, agree, clear = helpers.compare_trace(sub, out, cfg["vocab_size"], ref)
         assert worst <= tol, f"family {tag!r}: error {worst:.3g} of the logit scale at (step, request, position) {where}"
         if dtype == "float32":
             assert agree == 1.0, f"family {tag!r}: greedy tokens differ from the plain implementation"
+        else:
+            assert agree >= BF16_TOP1 and clear == 1.0, f"family {tag!r}: top-1 agreement {agree:.3f} ({clear:.3f} where clear)"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -53,7 +59,7 @@ def test_long_decoding_one_token_at_a_time(dtype, tiny_models, tmp_path):
     ref = {k: P.forward(helpers.read_weights(d), cfg, v) for k, v in seq.items()}
     steps = helpers.trace_tail(seq, tail=412)
     steps, out = helpers.run_trace(d, dtype, steps, str(tmp_path), 448, page)
-    worst, where, agree = helpers.compare_trace(steps, out, cfg["vocab_size"], ref)
+    worst, where, agree, clear = helpers.compare_trace(steps, out, cfg["vocab_size"], ref)
     assert worst <= (helpers.FP32_TOL if dtype == "float32" else helpers.BF16_TOL), (worst, where)
     assert agree == 1.0 if dtype == "float32" else agree > 0.97
 
@@ -69,8 +75,10 @@ def test_first_tokens_of_sequences(name, dtype, tiny_models, tmp_path):
                  "end": [f"g{k}" for k in seqs]}]
     steps = helpers.trace_whole(seqs, tag="w") + together + helpers.trace_tail(seqs, tail=3, tag="t")
     steps, out = helpers.run_trace(d, dtype, steps, str(tmp_path), 256, page)
-    worst, where, agree = helpers.compare_trace(steps, out, cfg["vocab_size"], ref)
+    worst, where, agree, clear = helpers.compare_trace(steps, out, cfg["vocab_size"], ref)
     assert worst <= (helpers.FP32_TOL if dtype == "float32" else helpers.BF16_TOL), (worst, where)
+    # twenty-one places only, some of them near-ties: in bfloat16 the floor holds where the plain lead is clear
+    assert (agree == 1.0 if dtype == "float32" else True) and clear == 1.0, (agree, clear)
 
 
 @pytest.mark.parametrize("name", sorted(helpers.MORE))
@@ -89,8 +97,9 @@ def test_other_geometries(name, tmp_path):
         numbered, out = helpers.run_trace(d, dtype, steps, str(tmp_path / dtype), max_tokens, page)
         for tag in families:
             sub = [s for s in numbered if s["entries"][0]["id"].startswith(tag)]
-            worst, where, agree = helpers.compare_trace(sub, out, cfg["vocab_size"], ref)
+            worst, where, agree, clear = helpers.compare_trace(sub, out, cfg["vocab_size"], ref)
             assert worst <= tol, f"{dtype}, family {tag!r}: error {worst:.3g} of the logit scale at {where}"
+            assert agree >= (1.0 if dtype == "float32" else BF16_TOP1) and clear == 1.0, (dtype, tag, agree, clear)
 
 
 @pytest.mark.parametrize("name,blocks", [("B", 3), ("C", 10)])
@@ -118,8 +127,9 @@ def test_decode_steps_on_the_large_batch_kernel(name, blocks, tiny_models, refer
                                    env={"ATOMA_INFER_DECODE_FLAT": str(blocks)})
     for tag in families:
         sub = [s for s in steps if s["entries"][0]["id"].startswith(tag)]
-        worst, where, agree = helpers.compare_trace(sub, out, cfg["vocab_size"], ref)
+        worst, where, agree, clear = helpers.compare_trace(sub, out, cfg["vocab_size"], ref)
         assert worst <= helpers.BF16_TOL, f"family {tag!r}: error {worst:.3g} of the logit scale at {where}"
+        assert agree >= BF16_TOP1 and clear == 1.0, (tag, agree, clear)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -139,7 +149,7 @@ def test_a_long_prompt(dtype, tiny_models, tmp_path):
     for i in range(2040, 2048):
         steps.append({"entries": [{"id": f"c{k}", "tokens": [v[i]], "want": [0]}], "end": [f"c{k}"] if i == 2047 else []})
     steps, out = helpers.run_trace(d, dtype, steps, str(tmp_path), 2048, page)
-    worst, where, agree = helpers.compare_trace(steps, out, cfg["vocab_size"], ref)
+    worst, where, agree, clear = helpers.compare_trace(steps, out, cfg["vocab_size"], ref)
     assert worst <= (5e-5 if dtype == "float32" else helpers.BF16_TOL), (worst, where)
 
 
@@ -152,5 +162,5 @@ def test_replay_beyond_the_configured_positions(tmp_path):
     ref = {k: P.forward(helpers.read_weights(d), cfg, v) for k, v in seqs.items()}
     steps = helpers.trace_tail(seqs, tail=40)
     steps, out = helpers.run_trace(d, "float32", steps, str(tmp_path / "out"), 128, 4)
-    worst, where, agree = helpers.compare_trace(steps, out, cfg["vocab_size"], ref)
+    worst, where, agree, clear = helpers.compare_trace(steps, out, cfg["vocab_size"], ref)
     assert worst <= helpers.FP32_TOL and agree == 1.0, (worst, where)
