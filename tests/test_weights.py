@@ -31,6 +31,26 @@ def test_safetensors_round_trip(tmp_path):
         SafetensorsFile(str(tmp_path / "bad.safetensors"))
 
 
+def test_safetensors_files_agree_with_the_format_library_both_ways(tmp_path):
+    """Files written here are read by the ``safetensors`` package (the format's own library) and files it
+    writes are read here, tensor for tensor: the round trip above alone would also pass with a private
+    format.  Skipped where the package is not installed."""
+    st = pytest.importorskip("safetensors.torch")
+    t = {"w.a": torch.randn(4, 6), "w.b": torch.randn(5, 3).to(torch.bfloat16), "n": torch.randn(9).to(torch.float16),
+         "i": torch.arange(12, dtype=torch.int32).reshape(3, 4), "s": torch.tensor(2.5)}
+    ours, theirs = str(tmp_path / "ours.safetensors"), str(tmp_path / "theirs.safetensors")
+    write_safetensors(ours, t, {"format": "pt"})
+    back = st.load_file(ours)
+    assert sorted(back) == sorted(t)
+    for n in t:
+        assert back[n].dtype == t[n].dtype and back[n].shape == t[n].shape and torch.equal(back[n], t[n])
+    st.save_file(t, theirs, metadata={"format": "pt"})
+    f = SafetensorsFile(theirs)
+    assert sorted(f.names()) == sorted(t) and f.metadata == {"format": "pt"}
+    for n in t:
+        assert f.dtype(n) == t[n].dtype and tuple(f.shape(n)) == tuple(t[n].shape) and torch.equal(f.tensor(n), t[n])
+
+
 def test_random_model_is_seeded_and_loads(tmp_path):
     a, b, c = (str(tmp_path / n) for n in "abc")
     write_random_model(a, helpers.CONFIG_A, 0)
