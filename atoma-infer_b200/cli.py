@@ -31,6 +31,8 @@ def _engine_flags(ap):
     ap.add_argument("--enable-chunked-prefill", dest="enable_chunked_prefill", action="store_true", default=None)
     ap.add_argument("--no-enable-chunked-prefill", dest="enable_chunked_prefill", action="store_false")
     ap.add_argument("--no-cuda-graphs", dest="cuda_graphs", action="store_false", default=None)
+    ap.add_argument("--random-weights", dest="random_weights_seed", type=int, metavar="SEED",
+                    help="the model folder holds only config.json: draw every tensor on the device from this seed")
 
 
 def _engine_config(args):
@@ -38,7 +40,7 @@ def _engine_config(args):
 
     cfg = EngineConfig.from_toml(args.config_path) if args.config_path else EngineConfig()
     for k in ("dtype", "block_size", "gpu_memory_utilization", "num_gpu_blocks_override", "max_num_batched_tokens",
-              "max_num_sequences", "max_model_len", "enable_chunked_prefill", "cuda_graphs"):
+              "max_num_sequences", "max_model_len", "enable_chunked_prefill", "cuda_graphs", "random_weights_seed"):
         v = getattr(args, k, None)
         if v is not None:
             setattr(cfg, k, v)

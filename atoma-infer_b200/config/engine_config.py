@@ -49,6 +49,9 @@ class EngineConfig:
     max_total_tokens: Optional[int] = None
     # decode steps replay a captured CUDA graph per padded batch size
     cuda_graphs: bool = True
+    # random-weights mode: the model folder needs only config.json, tensors are drawn on the device
+    random_weights_seed: Optional[int] = None
+    random_weights_std: float = 0.02
 
     def __post_init__(self):
         self.dtype = canonical_dtype(self.dtype)

@@ -171,6 +171,16 @@ static int g_ksplit_override = 0;
 // For tuning: a fixed number of K splits (0: chosen from the number of tiles, as usual).
 extern "C" void linear_skinny_set_ksplit(int k) { g_ksplit_override = k; }
 
+namespace {
+int device_sms() {  // multiprocessors of the current device
+    static int sms[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 132;
+    if (!sms[dev] && cudaDeviceGetAttribute(&sms[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms[dev] = 132;
+    return sms[dev];
+}
+}  // namespace
+
 // x [M, K] and w [N, K] bfloat16, rows 16-byte aligned (K % 8 == 0); M <= 16.
 extern "C" int linear_skinny(const void* x, const void* w, void* y, int out_dtype, int epilogue, const int* meta,
                              int use_rows, int M, int N, int K, cudaStream_t stream) {
@@ -183,7 +193,7 @@ extern "C" int linear_skinny(const void* x, const void* w, void* y, int out_dtyp
     const int n_out = epilogue == 1 ? N / 2 : N;
     const int tiles = epilogue == 1 ? (n_out + 7) / 8 : (N + 15) / 16;
     // Too few tiles to fill the GPU: clusters of blocks split K (at least one 32-wide k block per warp each).
-    int sms = 148;
+    const int sms = device_sms();
     int ksplits = (2 * sms + tiles - 1) / tiles;
     if (g_ksplit_override > 0) ksplits = g_ksplit_override;
     ksplits = max(1, min(min(ksplits, 8), ((K + 31) / 32) / SM_WARPS));

@@ -84,7 +84,8 @@ class Engine:
             page_size=cfg.block_size,
             num_pages=cfg.num_gpu_blocks_override, max_seqs=cfg.max_num_sequences,
             gpu_memory_utilization=cfg.gpu_memory_utilization, cuda_graphs=cfg.cuda_graphs,
-            max_model_len=cfg.max_model_len, max_batched_tokens=cfg.max_num_batched_tokens)
+            max_model_len=cfg.max_model_len, max_batched_tokens=cfg.max_num_batched_tokens,
+            random_weights_seed=cfg.random_weights_seed, random_weights_std=cfg.random_weights_std)
         spec = self.lm.model.spec
         self.max_model_len = min(cfg.max_model_len or spec.max_position or 2 ** 31, spec.max_position or 2 ** 31)
         self.scheduler = Scheduler(self.lm.manager, max_num_batched_tokens=cfg.max_num_batched_tokens,

@@ -21,6 +21,7 @@ from ..csrc.ops import CudaOps
 from ..parts.base import Runtime
 from ..parts.model import DecoderModel
 from ..weights.loader import load_tensors
+from ..weights.random_init import random_tensors
 from .step import StepFunction
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
@@ -64,14 +65,21 @@ def step_workspace_bytes(model: DecoderModel, dtype: torch.dtype, max_batched_to
 def load_model(model_dir: str, *, dtype: str = "bfloat16", device=None, page_size: int = 16,
                num_pages: Optional[int] = None, max_seqs: int = 64, gpu_memory_utilization: float = 0.9,
                poison_cache: bool = False, ops=None, cuda_graphs: bool = False,
-               max_model_len: Optional[int] = None, max_batched_tokens: int = 2048) -> LoadedModel:
+               max_model_len: Optional[int] = None, max_batched_tokens: int = 2048,
+               random_weights_seed: Optional[int] = None, random_weights_std: float = 0.02) -> LoadedModel:
     """``num_pages``: usable pages per pool; None sizes the pools from free device memory, leaving room for
-    the state slots of ``max_seqs`` requests and for the working memory of a step of ``max_batched_tokens``."""
+    the state slots of ``max_seqs`` requests and for the working memory of a step of ``max_batched_tokens``.
+    ``random_weights_seed``: the folder needs only its config.json; every tensor the model declares is drawn on
+    the device from that seed (what ``write_random_model`` draws on the same device with it)."""
     arch, config = architecture_of(model_dir)
     spec = arch.build_spec(config)
     model = DecoderModel(spec)
     rt = make_runtime(dtype, device, ops)
-    tensors = load_tensors(model_dir, model.declare(), dtype=rt.dtype, device=rt.device, ignore=spec.ignored_tensors)
+    if random_weights_seed is None:
+        tensors = load_tensors(model_dir, model.declare(), dtype=rt.dtype, device=rt.device, ignore=spec.ignored_tensors)
+    else:
+        tensors = random_tensors(model.declare(), random_weights_seed, std=random_weights_std, dtype=rt.dtype,
+                                 device=rt.device)
     model.bind(tensors, rt)
     del tensors
     groups = model.groups

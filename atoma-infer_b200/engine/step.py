@@ -14,6 +14,7 @@ prompt against its cached part (models/src/flash_attention.rs:384-410).
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -243,8 +244,18 @@ class StepFunction:
                     self._graph_pool = torch.cuda.graph_pool_handle()
                 # one pool for all graphs: only one replays at a time and its logits are consumed (sampled or
                 # copied) on the same stream before the next replay, so their activations may share memory
-                with torch.cuda.graph(graph, pool=self._graph_pool):
-                    g.logits = self.model.forward(ctx, self.cache, rows, bucket)
+                # Garbage that holds captured graphs of an engine no longer in use must not be collected while
+                # this capture runs (destroying a graph then invalidates the capture): collect it now, and keep the
+                # collector off until the capture has ended.
+                gc.collect()
+                gc_was_on = gc.isenabled()
+                gc.disable()
+                try:
+                    with torch.cuda.graph(graph, pool=self._graph_pool):
+                        g.logits = self.model.forward(ctx, self.cache, rows, bucket)
+                finally:
+                    if gc_was_on:
+                        gc.enable()
                 g.kernels = self.rt.ops.launches - before  # own kernels in one replay
                 g.graph = graph
                 graph.replay()

@@ -34,6 +34,128 @@ MODEL = {  # Llama 3.2 1B
 }
 PROMPT_LEN, PREFILL_TOKENS, PAGE = 2048, 2048, 16
 
+_LLAMA3 = {"architectures": ["LlamaForCausalLM"], "vocab_size": 128256, "num_key_value_heads": 8, "head_dim": 128,
+           "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "max_position_embeddings": 131072, "bos_token_id": 128000,
+           "eos_token_id": 128001}
+# The larger configurations with their serving workloads: requests, prompt lengths and new tokens (uniform, both
+# ends included), seed, temperature, token budget of a step.
+WORKLOADS = {
+    "3b": {"config": dict(_LLAMA3, hidden_size=3072, intermediate_size=8192, num_hidden_layers=28, num_attention_heads=24,
+                          tie_word_embeddings=True,
+                          rope_scaling={"factor": 32.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                        "original_max_position_embeddings": 8192, "rope_type": "llama3"}),
+           "name": "Llama-3.2-3B", "requests": 16, "prompt": (256, 2048), "new": (256, 256), "seed": 3,
+           "temperature": None, "budget": 2048},
+    "8b": {"config": dict(_LLAMA3, hidden_size=4096, intermediate_size=14336, num_hidden_layers=32, num_attention_heads=32,
+                          tie_word_embeddings=False,
+                          rope_scaling={"factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                                        "original_max_position_embeddings": 8192, "rope_type": "llama3"}),
+           "name": "Llama-3.1-8B", "requests": 64, "prompt": (128, 4096), "new": (128, 512), "seed": 4,
+           "temperature": 0.7, "budget": 2048},
+}
+
+
+def serving_workload(which: str) -> int:
+    """A larger configuration with its serving workload through ``Engine.generate`` (random weights drawn on the
+    device; scheduler, chunked prefill, mixed steps, decode graphs).  Run twice: once as a user would, for the
+    end-to-end rate; once with a synchronisation after every step, to split the time into decode-only steps
+    (bytes they must read against the copy bandwidth) and steps that carry prompt tokens (flops against the
+    tensor peak).  Prints one JSON line."""
+    import tempfile
+    import time
+
+    import torch
+
+    import atoma_infer_b200  # noqa: F401
+    from atoma_infer_b200.engine import Engine
+    from atoma_infer_b200.sampling import SamplingParams
+
+    wl = WORKLOADS[which]
+    cfg = wl["config"]
+    hbm_gbs, bf16_tflops, peak_kind = peaks()
+    g = torch.Generator().manual_seed(wl["seed"])
+    n = wl["requests"]
+    plens = torch.randint(wl["prompt"][0], wl["prompt"][1] + 1, (n,), generator=g).tolist()
+    news = torch.randint(wl["new"][0], wl["new"][1] + 1, (n,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg["vocab_size"], (p,), generator=g).tolist() for p in plens]
+    params = [SamplingParams(do_sample=wl["temperature"] is not None, temperature=wl["temperature"], random_seed=100 + i,
+                             max_new_tokens=m, ignore_eos_token=True) for i, m in enumerate(news)]
+    L, H, I, V = cfg["num_hidden_layers"], cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    lin_params = L * (H * (nq + 2 * nkv) * d + nq * d * H + 3 * H * I)
+    head_params = V * H
+    weight_bytes = 2 * (lin_params + head_params)  # decode reads every linear once and the head; no embedding rows to speak of
+    kv_bytes_per_token = 2 * L * nkv * d * 2
+    pages = sum(-(-(p + m) // PAGE) for p, m in zip(plens, news)) + 64
+    with tempfile.TemporaryDirectory() as tmp:
+        with open(os.path.join(tmp, "config.json"), "w") as f:
+            json.dump(cfg, f)
+        eng = Engine(tmp, dtype="bfloat16", block_size=PAGE, num_gpu_blocks_override=pages, max_num_sequences=n,
+                     max_num_batched_tokens=wl["budget"], random_weights_seed=0)
+    lm = eng.lm
+    eng.generate([prompts[0][:64]], SamplingParams(do_sample=False, max_new_tokens=4, ignore_eos_token=True))  # libraries load
+    clocks = ClockSampler()
+    clocks.start()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = eng.generate(prompts, params)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    steps_e2e, launches = eng.num_steps, lm.rt.ops.launches
+    generated = sum(len(o.token_ids) for o in outs)
+    assert [len(o.token_ids) for o in outs] == news
+    # second run, a synchronisation after every step
+    rec = {"decode": [0, 0.0, 0.0, 0], "mixed": [0, 0.0, 0.0, 0]}  # steps, seconds, bytes or flops, tokens
+    run = lm.step.run
+
+    def timed(entries):
+        ctx = [lm.manager.num_tokens(e.req) if lm.manager.has_request(e.req) else 0 for e in entries]
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        out = run(entries)
+        b.record()
+        torch.cuda.synchronize()
+        dt = a.elapsed_time(b) * 1e-3  # device time of the step, launch gaps of prompt steps included
+        toks = sum(len(e.tokens) for e in entries)
+        if all(len(e.tokens) == 1 for e in entries):
+            r = rec["decode"]
+            r[2] += weight_bytes + kv_bytes_per_token * sum(c + 1 for c in ctx)
+        else:
+            r = rec["mixed"]
+            attn = sum(4 * d * nq * L * (len(e.tokens) * c + len(e.tokens) * (len(e.tokens) + 1) // 2) for e, c in zip(entries, ctx))
+            r[2] += 2 * toks * lin_params + attn + 2 * head_params * sum(1 for e in entries if e.want)
+        r[0] += 1
+        r[1] += dt
+        r[3] += toks
+        return out
+
+    lm.step.run = timed
+    eng.generate(prompts, params)
+    lm.step.run = run
+    clock_rec = clocks.stop()
+    dec, mix = rec["decode"], rec["mixed"]
+    out = {
+        "metric": f"generated tok/s through Engine.generate ({wl['name']} sizes, {n} requests)", "value": generated / wall,
+        "unit": "tok/s", "n_gpus": 1, "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "vs_baseline": None, "seconds": wall, "total_tok_s": (generated + sum(plens)) / wall, "steps": steps_e2e,
+        "prompt_tokens": sum(plens), "generated_tokens": generated, "preemptions": eng.scheduler.num_preemptions,
+        "gpu_launches": launches,
+        "config": {"model": f"{wl['name']} (random weights N(0,0.02), seed 0)", "layers": L, "hidden": H, "heads": nq,
+                   "kv_heads": nkv, "head_dim": d, "intermediate": I, "vocab": V, "requests": n,
+                   "prompt_lengths": f"uniform {wl['prompt']}, seed {wl['seed']}", "new_tokens": f"uniform {wl['new']}",
+                   "temperature": wl["temperature"], "token_budget": wl["budget"], "page_size": PAGE, "parallelism": "1 GPU"},
+        "decode_steps": {"steps": dec[0], "ms_per_step": dec[1] / max(dec[0], 1) * 1e3, "tokens_per_step": dec[3] / max(dec[0], 1),
+                         "achieved": dec[2] / max(dec[1], 1e-9) / 1e9, "peak": hbm_gbs, "unit": "GB/s",
+                         "frac": dec[2] / max(dec[1], 1e-9) / 1e9 / hbm_gbs, "of": peak_kind},
+        "prompt_steps": {"steps": mix[0], "ms_per_step": mix[1] / max(mix[0], 1) * 1e3, "tokens_per_step": mix[3] / max(mix[0], 1),
+                         "achieved": mix[2] / max(mix[1], 1e-9) / 1e12, "peak": bf16_tflops, "unit": "TFLOP/s",
+                         "frac": mix[2] / max(mix[1], 1e-9) / 1e12 / bf16_tflops, "of": f"{peak_kind} bf16 burst"},
+        "clocks": clock_rec,
+    }
+    print(json.dumps(out))
+    return 0
+
 
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -89,6 +211,10 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=MODEL["num_hidden_layers"],
                     help="fewer layers than the model has (both numbers are reported)")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--model", default="1b", choices=["1b", "3b", "8b"],
+                    help="1b: the headline benchmark; 3b / 8b: the larger configurations with their serving workloads")
+    ap.add_argument("--context", type=int, default=PROMPT_LEN,
+                    help="prompt length of the decode measurements (default 2,048; 8,192 and 32,768 for long contexts)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--phase", default="all", choices=["all", "prefill", "decode"],
                     help="measure only one phase (for profiling); the JSON line then lacks the other")
@@ -104,6 +230,8 @@ def main() -> int:
             print(f"bench.py measures a one-GPU engine; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.model != "1b":
+        return serving_workload(args.model)
 
     import torch
 
@@ -127,7 +255,8 @@ def main() -> int:
     kv_bytes_per_token = 2 * L * nkv * d * 2
 
     max_batch = 64 if not args.skip_points else args.batch
-    tokens_per_req = PROMPT_LEN + 5 * args.steps + args.warmup + 64
+    prompt_len = args.context
+    tokens_per_req = prompt_len + 5 * args.steps + args.warmup + 64
     pages = max_batch * (-(-tokens_per_req // PAGE)) + 256
     eng = Engine(tmp, dtype="bfloat16", block_size=PAGE, num_gpu_blocks_override=pages,
                  max_num_sequences=max(max_batch, 8), max_num_batched_tokens=max(PREFILL_TOKENS, max_batch))
@@ -136,7 +265,7 @@ def main() -> int:
     greedy = SamplingParams(do_sample=False, max_new_tokens=10 ** 6, ignore_eos_token=True)
 
     def prompt():
-        return torch.randint(0, V, (PROMPT_LEN,), generator=g).tolist()
+        return torch.randint(0, V, (prompt_len,), generator=g).tolist()
 
     def event_ms(fn):
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -148,7 +277,7 @@ def main() -> int:
         return a.elapsed_time(b)
 
     # ------------------------------------------------------------------ prefill of 2,048 tokens
-    toks = prompt()
+    toks = torch.randint(0, V, (PREFILL_TOKENS,), generator=g).tolist()
     times = []
     for i in range(3 + 5 if args.phase != "decode" else 0):
         req = 10 ** 6 + i
@@ -168,7 +297,7 @@ def main() -> int:
         """Prefills ``batch`` requests, warms up, then times ``steps`` decode steps REPEATS times over (the
         context grows from one repeat to the next).  Returns a record of the median repeat."""
         ids = [eng.add_request(prompt(), greedy) for _ in range(batch)]
-        while any(eng.scheduler.num_computed(i) < PROMPT_LEN for i in ids):
+        while any(eng.scheduler.num_computed(i) < prompt_len for i in ids):
             eng.step()  # prompts in portions under the token budget; the last portion samples
         for _ in range(warmup):
             eng.step()
@@ -236,7 +365,8 @@ def main() -> int:
         "config": {
             "model": "Llama-3.2-1B (random weights N(0,0.02), seed 0)", "layers": L,
             "layers_full": MODEL["num_hidden_layers"], "hidden": H, "heads": nq, "kv_heads": nkv, "head_dim": d,
-            "intermediate": I, "vocab": V, "global_batch": args.batch, "seq_len": PROMPT_LEN, "context": 4096,
+            "intermediate": I, "vocab": V, "global_batch": args.batch, "seq_len": prompt_len,
+            "context": 4096 if prompt_len == PROMPT_LEN else prompt_len + 5 * args.steps + args.warmup,
             "page_size": PAGE, "parallelism": "1 GPU", "repeats": f"median of {REPEATS} regions of --steps steps each",
             "l2": "inputs larger than L2 (2.47 GB of weights read every step)", "prompt_ids": "uniform, seed 2",
         },
