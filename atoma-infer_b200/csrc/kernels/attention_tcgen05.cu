@@ -253,16 +253,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     const bool any_bad = __syncthreads_or(bad) != 0;  // a table with holes where keys should be: every tile checks its V rows
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-#ifdef ATTN_TC_PROFILE  // clock stamps of one thread of one block (1: a softmax thread, 2: the MMA thread, 3: the copy warp)
-    long long* prof = reinterpret_cast<long long*>(status + 16);
-    const bool prof_on = blockIdx.y == 20 && blockIdx.x == 0 && blockIdx.z == 0 &&
-                         tid == (ATTN_TC_PROFILE == 1 ? 33 : ATTN_TC_PROFILE == 2 ? MMA_WARP * 32 : COPY_WARP * 32);
-    int prof_i = 0;
-#define PROF() do { if (prof_on && prof_i < 120) prof[prof_i++] = clock64(); } while (0)
-#else
-#define PROF() do {} while (0)
-#endif
-    PROF();
 
     if (warp >= SOFTMAX_WARPS) {
         if (D == 64) regs_release<32>();
@@ -292,16 +282,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
             for (int t = 0; t + 2 < ntiles; ++t) {
                 const int b = t & 1;
                 const uint32_t par = (uint32_t)(t >> 1) & 1u;
-                PROF();
                 ok = mbar_wait(&s_done[b], par, status, abort_flag);  // the scores of tile t are done: its K stage is free
                 if (!ok) break;
-                PROF();
                 issue_loads(t + 2, 0, k_s + b * STAGE, &k_full[b]);
                 last_k[b] = t + 2;
-                PROF();
                 ok = mbar_wait(&o_done[b], par, status, abort_flag);  // P V of tile t is done: its V stage is free
                 if (!ok) break;
-                PROF();
                 issue_loads(t + 2, 1, v_s + b * STAGE, &v_full[b]);
                 last_v[b] = t + 2;
             }
@@ -336,7 +322,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
             for (int t = 0; t < ntiles && ok; ++t) {
                 const int b = t & 1;
                 const uint32_t par = (uint32_t)(t >> 1) & 1u;
-                PROF();
                 if (t >= 1 && t + 1 < ntiles) {
                     // the other buffer: the softmax warps take its last product (tile t - 1) in the middle of
                     // this tile's softmax; then the scores of tile t + 1 may overwrite it
@@ -345,10 +330,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
                     issue_scores(t + 1);
                     if (!ok) break;
                 }
-                PROF();
                 ok = mbar_wait(&p_ready[b], par, status, abort_flag);  // P(t) is in tensor memory, V(t) is whole
                 if (!ok) break;
-                PROF();
                 ok = mbar_wait(&v_full[b], par, status, abort_flag);
                 if (!ok) break;
                 tc_fence_after();
@@ -359,7 +342,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
                                      idesc_o, ks > 0);
                 }
                 umma_commit(&o_done[b]);
-                PROF();
             }
         }
     } else {
@@ -399,10 +381,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
             const int b = t & 1;
             const uint32_t par = (uint32_t)(t >> 1) & 1u;
             const uint32_t tmem_buf = tmem_row + b * BUF_COLS;
-            PROF();
             if (!mbar_wait(&s_done[b], par, status, abort_flag)) ok = false;
             tc_fence_after();
-            PROF();
 
             // ---- softmax of my half row, in two passes over its 64 scores in tensor memory (16 at a time, so
             // that few registers are live): first the maximum, then the exponentials
@@ -459,7 +439,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
             l_run = l_run * corr + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             m_run = m_new;
             corr_prev = corr;
-            PROF();
 
             // ---- V rows that no page delivered, or that lie beyond the last key, must be zero (0 * NaN would
             // poison P V): the last tile, a tile that starts before the window, a block table with holes
@@ -479,7 +458,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&p_ready[b]);
-            PROF();
         }
         if (ntiles > 0) add_product(ntiles - 1);
 

@@ -168,7 +168,7 @@ linear_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __
 }
 
 static int g_ksplit_override = 0;
-// For tuning: a fixed number of K splits (0: chosen from the number of tiles, as usual).
+// For the kernel tests: a fixed number of K splits (0: chosen from the number of tiles, as usual).
 extern "C" void linear_skinny_set_ksplit(int k) { g_ksplit_override = k; }
 
 namespace {

@@ -60,9 +60,10 @@ class CudaOps:
         self.launches = 0  # own kernel launches, counted for the benchmark record
         self._attn_libs = {}
         self._attn_tc_libs = {}
-        self.tc_attention = os.environ.get("ATOMA_INFER_TC_ATTENTION", "1") != "0"  # tcgen05 prefill attention
-        self.decode_cluster = os.environ.get("ATOMA_INFER_DECODE_CLUSTER", "1") != "0"  # split merge inside a cluster
-        self.tc_gemm = os.environ.get("ATOMA_INFER_TC_GEMM", "1") != "0"  # gate/up + SwiGLU of long prompts on tcgen05
+        # levers for the kernel tests (each kernel is compared with the one it stands in for)
+        self.tc_attention = True    # tcgen05 prefill attention where the geometry allows
+        self.decode_cluster = True  # split merge of the decode attention inside a cluster
+        self.tc_gemm = True         # gate/up + SwiGLU of long prompts on tcgen05
         # large decode batches: key tiles dealt out evenly over as many blocks as the GPU holds ("0": never;
         # a number above 1: always, with that many blocks, for experiments and tests)
         flat = os.environ.get("ATOMA_INFER_DECODE_FLAT", "1")
@@ -83,7 +84,7 @@ class CudaOps:
         # ATOMA_INFER_PDL: "0" off, "1" every kernel, "linear" without the norm, default "linear+norm".
         mode = os.environ.get("ATOMA_INFER_PDL", "linear+norm")
         self.pdl = {"0": 0, "1": 1, "linear": 2, "linear+norm": 6}.get(mode, 6)
-        self.fused_rope = os.environ.get("ATOMA_INFER_FUSED_ROPE", "1") != "0"
+        self.fused_rope = True  # the decode attention rotates q and k and writes the new key and value itself
         self.lib.kernels_set_pdl(int(self.pdl))
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
 
@@ -312,8 +313,6 @@ class CudaOps:
             lib.attn_decode_scratch_floats.restype = ctypes.c_size_t
             lib.attn_decode_flat_scratch_floats.restype = ctypes.c_size_t
             lib.kernels_set_pdl(1 if self.pdl else 0)
-            # page loads of the decode kernel by TMA: measured no faster than cp.async (13.1 vs 15.4 us at batch 8), so opt-in
-            lib.attn_set_decode_tma(int(os.environ.get("ATOMA_INFER_DECODE_TMA", "0") == "1"))
             if lib.attn_head_dim() != d:
                 raise KernelError(f"attention library was built for head size {lib.attn_head_dim()}, wanted {d}")
             self._attn_libs[d] = lib

@@ -125,6 +125,27 @@ def test_bfloat16_linear_all_row_counts(rts, M, N, Kd):
     assert y32.dtype == torch.float32 and (y32.double().cpu() - want).abs().max() < 2e-3  # float32 accumulation kept
 
 
+@pytest.mark.parametrize("M,N,Kd", [(5, 272, 2048), (16, 64, 8192), (1, 1000, 4096)])
+def test_few_row_linear_with_every_split_of_k(rts, M, N, Kd):
+    """The blocks of a cluster split K when a matrix has few 16-row tiles (the engine picks the count from the
+    number of tiles); here every count is forced in turn, the leader adding the others' partial sums from their
+    shared memory.  All give the product, and a given count the same bits twice."""
+    rt = rts["bfloat16"]
+    g = torch.Generator().manual_seed(N)
+    x = torch.randn(M, Kd, generator=g).bfloat16()
+    w = (torch.randn(N, Kd, generator=g) / math.sqrt(Kd)).bfloat16()
+    want = x.double() @ w.double().T
+    xd, wd = x.to(rt.device), w.to(rt.device)
+    try:
+        for splits in range(1, 9):
+            rt.ops.lib.linear_skinny_set_ksplit(splits)
+            y = rt.ops.linear(xd, wd, out_dtype=torch.float32)
+            assert (y.double().cpu() - want).abs().max() < 2e-3, splits
+            assert torch.equal(y, rt.ops.linear(xd, wd, out_dtype=torch.float32)), splits
+    finally:
+        rt.ops.lib.linear_skinny_set_ksplit(0)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M", [2, 8, 13, 33])
 def test_swiglu_gate_epilogue(rts, dtype, M):
