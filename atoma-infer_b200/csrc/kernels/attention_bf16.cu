@@ -247,14 +247,17 @@ namespace {
 constexpr int DEC_KT = 32;                       // keys per warp tile
 constexpr int DEC_NK = DEC_KT / 8;
 constexpr int DEC_WARPS = 4;
-constexpr int DEC_STAGES = D <= 128 ? 2 : 1;
+constexpr int DEC_STAGES = D <= 64 ? 2 : 1;  // above 64 one stage: more blocks a multiprocessor beat a second stage (head size 128: 2.3 -> 3.8 TB/s at 16 requests)
 constexpr int DEC_WARP_ELEMS = DEC_STAGES * 2 * DEC_KT * LDS;  // bf16 elements of one warp's K/V stages
 constexpr size_t DEC_MERGE_BYTES = (size_t)DEC_WARPS * (32 + 16 * D) * sizeof(float);
-constexpr size_t DEC_MAIN_BYTES = 16 * LDS * sizeof(bf16) +
-    (DEC_WARPS * DEC_WARP_ELEMS * sizeof(bf16) > DEC_MERGE_BYTES ? DEC_WARPS * DEC_WARP_ELEMS * sizeof(bf16) : DEC_MERGE_BYTES);
 constexpr int DEC_MAX_CLUSTER = 8;                     // splits that can merge through the cluster's shared memory
 constexpr size_t DEC_SHARE_BYTES = (size_t)(16 * D + 32) * sizeof(float);  // a block's result for its cluster: o[16][D], (m, l)[16]
-constexpr size_t DEC_SMEM = DEC_MAIN_BYTES + DEC_SHARE_BYTES;
+// The query tile, then one region that holds the warps' key/value stages while keys are walked and afterwards the
+// warps' partial results (the merge buffer) followed by the block's result for its cluster.
+constexpr size_t DEC_MAIN_BYTES = 16 * LDS * sizeof(bf16) +
+    (DEC_WARPS * DEC_WARP_ELEMS * sizeof(bf16) > DEC_MERGE_BYTES + DEC_SHARE_BYTES ? DEC_WARPS * DEC_WARP_ELEMS * sizeof(bf16)
+                                                                                   : DEC_MERGE_BYTES + DEC_SHARE_BYTES);
+constexpr size_t DEC_SMEM = DEC_MAIN_BYTES;
 constexpr int DEC_BLOCKS_PER_SM = (int)((227 * 1024) / (DEC_SMEM + 1024)) < 8 ? (int)((227 * 1024) / (DEC_SMEM + 1024)) : 8;
 }  // namespace
 
@@ -285,7 +288,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
     unsigned char* smem_al = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     bf16* qtile = reinterpret_cast<bf16*>(smem_al);
     bf16* tiles = qtile + 16 * LDS;
-    float* share = reinterpret_cast<float*>(smem_al + DEC_MAIN_BYTES);
+    float* share = reinterpret_cast<float*>(tiles) + DEC_WARPS * (32 + 16 * D);  // behind the merge buffer, once the stages are done
     __shared__ int s_last;
     __shared__ __align__(8) uint64_t tile_bar[DEC_WARPS][2];  // a warp's stage is full (TMA path)
     pdl_launch_dependents();
@@ -1177,8 +1180,22 @@ int g_decode_tma = 0;
 extern "C" void attn_set_decode_tma(int on) { g_decode_tma = on; }
 
 extern "C" int attn_head_dim() { return D; }
-// How many decode blocks fit a multiprocessor (by shared memory): the host sizes the splits by it.
-extern "C" int attn_decode_blocks_per_sm() { return DEC_BLOCKS_PER_SM; }
+// How many decode blocks a multiprocessor of the current device holds at once (shared memory and registers both
+// count: large heads are bound by registers); the host sizes the splits by it.
+extern "C" int attn_decode_blocks_per_sm() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return DEC_BLOCKS_PER_SM;
+    if (!cached[dev]) {
+        int n = 0;
+        const size_t smem = DEC_SMEM + 1024;
+        if (cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess ||
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attn_decode_kernel, DEC_WARPS * 32, smem) != cudaSuccess || n < 1)
+            n = DEC_BLOCKS_PER_SM;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
 // The most splits that can merge through a cluster's shared memory (the portable cluster size).
 extern "C" int attn_decode_max_cluster() { return DEC_MAX_CLUSTER; }
 

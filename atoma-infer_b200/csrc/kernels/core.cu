@@ -530,7 +530,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, c
     pdl_launch_dependents();
     pdl_wait();
     int t = blockIdx.y;
-    if (t >= meta[META_NUM_TOKENS]) return;
+    if (meta && t >= meta[META_NUM_TOKENS]) return;  // without step metadata every launched row is a real one
     constexpr int V = 16 / sizeof(T);  // elements of a 16-byte access
     const T* g = gu + (size_t)t * 2 * I;
     T* o = out + (size_t)t * I;
