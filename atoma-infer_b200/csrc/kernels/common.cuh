@@ -110,6 +110,37 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 
 #define LAUNCH_RETURN() return (int)cudaGetLastError()
 
+// ----------------------------------------------------------------------------- weights ahead of time
+// Up to four byte ranges that a kernel asks to be brought into L2 (a hint: nothing waits for it, the copies go on
+// underneath whatever runs).  The decode attention of a small batch leaves memory bandwidth unused; it asks for the
+// weights of the linear after it, which then streams them from L2.
+struct PrefetchRanges {
+    const char* ptr[4];
+    unsigned long long bytes[4];  // multiples of 16; 0: unused
+};
+// Every calling thread asks for its share; `n` threads call with i = 0 .. n-1.
+__device__ __forceinline__ void prefetch_ranges_l2(const PrefetchRanges& r, unsigned long long i, unsigned long long n) {
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        if (!r.bytes[s]) continue;
+        const unsigned long long share = (((r.bytes[s] + n - 1) / n) + 255) & ~255ull;
+        const unsigned long long begin = i * share, end = begin + share < r.bytes[s] ? begin + share : r.bytes[s];
+        for (unsigned long long off = begin; off < end; off += 4096) {
+            const unsigned len = (unsigned)(end - off < 4096ull ? end - off : 4096ull);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(r.ptr[s] + off), "r"(len) : "memory");
+        }
+    }
+}
+static inline PrefetchRanges make_prefetch_ranges(int n, const void* const* ptrs, const unsigned long long* bytes) {
+    PrefetchRanges r = {};
+    for (int i = 0; i < n && i < 4; ++i) {
+        if ((uintptr_t)ptrs[i] & 15) continue;
+        r.ptr[i] = (const char*)ptrs[i];
+        r.bytes[i] = bytes[i] & ~15ull;
+    }
+    return r;
+}
+
 // ----------------------------------------------------------------------------- dependent launches
 // Kernels of a step run back to back on one stream.  Launched with programmatic stream
 // serialization, a kernel may start while its predecessor is still draining: what it does

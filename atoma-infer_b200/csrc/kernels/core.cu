@@ -564,6 +564,18 @@ extern "C" int silu_mul(const void* gu, void* out, int dtype, const int* meta, i
                               meta, I);
 }
 
+// ----------------------------------------------------------------------------- weights ahead of time
+// A kernel of its own that only asks byte ranges into L2 (see PrefetchRanges) and ends at once.
+__global__ void l2_prefetch_kernel(const PrefetchRanges r) {
+    pdl_launch_dependents();
+    prefetch_ranges_l2(r, (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x, (unsigned long long)gridDim.x * blockDim.x);
+}
+extern "C" int l2_prefetch(int n, const void* const* ptrs, const unsigned long long* bytes, cudaStream_t stream) {
+    const PrefetchRanges r = make_prefetch_ranges(n, ptrs, bytes);
+    if (!(r.bytes[0] | r.bytes[1] | r.bytes[2] | r.bytes[3])) return 0;
+    return (int)launch_kernel(l2_prefetch_kernel, 64, 128, 0, stream, r);
+}
+
 // ----------------------------------------------------------------------------- casts
 template <typename TI, typename TO>
 __global__ void cast_kernel(const TI* __restrict__ in, TO* __restrict__ out, size_t n) {

@@ -53,6 +53,9 @@ class Attention(Mixer):
     def activation_width(self):
         return self.q_size + 2 * self.kv_size
 
+    def streamed_weights(self):
+        return [self.w_qkv, self.w_o]
+
     def cache_need(self):
         return CacheNeed.kv(self.num_kv_heads, self.head_dim, self.window)
 

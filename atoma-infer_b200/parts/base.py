@@ -91,6 +91,11 @@ class Part:
     def bind(self, tensors: Dict[str, torch.Tensor], rt: Runtime) -> None:
         self.rt = rt
 
+    def streamed_weights(self) -> List[torch.Tensor]:
+        """The weight matrices of the part's linears in the order ``forward`` uses them (after ``bind``).  The model
+        hands the whole step's list to the kernels, which may fetch a weight ahead of its use."""
+        return []
+
     def activation_width(self) -> int:
         """Elements per token of the widest intermediate result the part makes (0: nothing wider than the
         model's width); the engine sizes its working memory from it when it sizes the cache."""

@@ -27,6 +27,9 @@ class PreNormBlock(Block):
     def parts(self):
         return [self.norm1, self.mixer, self.norm2, self.feed_forward]
 
+    def streamed_weights(self):
+        return self.mixer.streamed_weights() + self.feed_forward.streamed_weights()
+
     def activation_width(self):
         return max(p.activation_width() for p in self.parts())
 

@@ -36,6 +36,9 @@ class SwiGLU(FeedForward):
         self.w_gate_up = torch.cat([tensors[pre + ".gate_proj.weight"], tensors[pre + ".up_proj.weight"]], 0).contiguous()
         self.w_down = tensors[pre + ".down_proj.weight"].contiguous()
 
+    def streamed_weights(self):
+        return [self.w_gate_up, self.w_down]
+
     def forward(self, x, ctx):
         ops = self.rt.ops
         act = ops.linear(x, self.w_gate_up, silu_mul=True, meta=ctx.meta)

@@ -33,6 +33,9 @@ class LinearHead(Head):
             if self.weight is None or tuple(self.weight.shape) != (self.vocab, self.hidden):
                 raise ValueError("a head without a matrix of its own needs an embedding with a [vocab, hidden] table")
 
+    def streamed_weights(self):
+        return [self.weight]
+
     def forward(self, h, ctx):
         return self.rt.ops.linear(h, self.weight, out_dtype=torch.float32, meta=ctx.meta, use_rows=True)
 

@@ -147,6 +147,9 @@ class DecoderModel:
             blk.bind(tensors, rt)
         self.final_norm.bind(tensors, rt)
         self.head.bind(tensors, rt, self.embedding)
+        if hasattr(rt.ops, "set_weight_order"):  # the step's weight stream, in order of use
+            order = [w for r in self.runs for w in self.blocks[r.layer].streamed_weights()]
+            rt.ops.set_weight_order(order + self.head.streamed_weights())
 
     # ------------------------------------------------------------------ the forward pass of one step
     def forward(self, ctx: StepContext, cache, rows: torch.Tensor, num_rows: int) -> torch.Tensor:
