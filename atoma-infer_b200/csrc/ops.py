@@ -360,15 +360,19 @@ class CudaOps:
 
     def decode_splits(self, S: int, nkv: int, max_context: int, blocks_per_sm: int = 2) -> int:
         """Splits of the key range per (request, key/value head) in a decode step.  Few requests:
-        as many splits as keep all blocks resident at once, at most 8 (every split costs an arrival
-        at the merge counter) and at least 256 keys each.  Many requests (more blocks than fit at
+        as many splits as keep all blocks resident at once, at most 8 (one cluster, which merges through its
+        shared memory) and at least 256 keys each; a long context of very few requests takes more than 8 (at
+        least 512 keys each, merged through scratch by the last block to arrive) when that at least doubles the
+        blocks (one request of 32,768 keys: 43 -> 25 us a layer).  Many requests (more blocks than fit at
         once): the smallest count up to 4 whose last wave is at least 85 % as full as the best
         (the reference's heuristic has this shape, csrc/src/lib.rs:2122-2199)."""
         blocks = max(S * nkv, 1)
         capacity = self.num_sms * max(blocks_per_sm, 1)
         most = max(1, max_context // 256)
         if blocks < capacity:
-            return max(1, min(8, most, capacity // blocks))
+            few = max(1, min(8, most, capacity // blocks))
+            many = min(capacity // blocks, max_context // 512)
+            return many if many >= 2 * few else few
 
         def efficiency(s):
             waves = blocks * s / capacity

@@ -57,7 +57,15 @@ def run_attention(rt, entries, nq, nkv, d, page_size, window=None, seed=0, scale
     got, want, row = [], [], 0
     for (c, n), q, k, v in zip(entries, qs, ks, vs):
         got.append(out[row:row + n].float().cpu().reshape(n, nq, d))
-        want.append(P.causal_attention(q.double(), k.double(), v.double(), scale, window)[c:c + n].float())
+        if n == 1 and c >= 2048:  # a long context and one query: the plain function on the last row alone (the whole
+            # score matrix of all rows would take gigabytes); rows before the last see nothing of it
+            first = max(0, c - window + 1) if window else 0
+            kk = k[first:c + 1].double().repeat_interleave(nq // nkv, dim=1)
+            vv = v[first:c + 1].double().repeat_interleave(nq // nkv, dim=1)
+            w = torch.softmax(torch.einsum("hd,shd->hs", q[c].double(), kk) * scale, dim=-1)
+            want.append(torch.einsum("hs,shd->hd", w, vv)[None].float())
+        else:
+            want.append(P.causal_attention(q.double(), k.double(), v.double(), scale, window)[c:c + n].float())
         row += n
     return got, want
 
@@ -90,6 +98,19 @@ def test_decode_with_splits_bf16(rts, d, nq, nkv, page, splits, cluster):
     finally:
         ops.decode_cluster = True
     assert worst(got, want) < 2e-2
+
+
+@pytest.mark.parametrize("d,nq,nkv", [(64, 32, 8), (128, 8, 2)])
+def test_decode_of_one_long_request_takes_many_splits(rts, d, nq, nkv):
+    """A long context of one or two requests is cut into more than eight splits (the engine's own choice, merged
+    through scratch memory by the last block to arrive); one key far back stands out, so a lost split would show."""
+    rt = rts["bfloat16"]
+    lib = rt.ops._attention_library(d)
+    for entries in ([(9000, 1)], [(9000, 1), (4100, 1)]):
+        splits = rt.ops.decode_splits(len(entries), nkv, 9001, lib.attn_decode_blocks_per_sm())
+        assert splits > 8, splits
+        got, want = run_attention(rt, entries, nq, nkv, d, 16, seed=7, stand_out=1234, scale=1.0)
+        assert worst(got, want) < 3e-2
 
 
 @pytest.mark.parametrize("blocks", [1, 2, 5, 37, 444])
