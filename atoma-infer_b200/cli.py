@@ -76,7 +76,9 @@ def _cmd_generate(args) -> int:
             "preemptions": m.num_preemptions,
         }))
     n = sum(len(o.token_ids) for o in outs)
-    print(f"{n} tokens generated ({n / dt:.1f} token/s), {eng.num_steps} steps", file=sys.stderr)
+    st = eng.stats()
+    print(f"{n} tokens generated ({n / dt:.1f} token/s), {st['steps']} steps ({st['graph_replays']} as graph replays), "
+          f"{st['preemptions']} preemptions, {st['kernel_launches']} kernel launches", file=sys.stderr)
     return 0
 
 

@@ -11,6 +11,8 @@ text is outside this engine.  A finished request's pages are given back at once.
 """
 from __future__ import annotations
 
+import contextlib
+import os
 import sys
 import time
 from dataclasses import dataclass, field
@@ -99,6 +101,13 @@ class Engine:
         self._next_id = 0
         self.num_steps = 0
         self.num_generated = 0
+        # Optional tracing (the reference has `tracing` spans around its worker and layers,
+        # backends/vllm/src/worker.rs:110): ATOMA_INFER_TRACE=1 prints every step's batch composition and, one step
+        # late so that nothing waits, its device time from a pair of CUDA events; ATOMA_INFER_NVTX=1 wraps plan,
+        # launch and read-back of a step in NVTX ranges for a timeline profiler.
+        self.trace = os.environ.get("ATOMA_INFER_TRACE", "0") not in ("", "0")
+        self.nvtx = os.environ.get("ATOMA_INFER_NVTX", "0") not in ("", "0") and torch.cuda.is_available()
+        self._trace_events = None
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt_token_ids: Sequence[int], params: Optional[SamplingParams] = None) -> int:
@@ -130,6 +139,37 @@ class Engine:
     def has_unfinished(self) -> bool:
         return self.scheduler.has_unfinished() or self._inflight is not None
 
+    # ------------------------------------------------------------------ tracing
+    def _range(self, name: str):
+        return torch.cuda.nvtx.range(name) if self.nvtx else contextlib.nullcontext()
+
+    def _trace_step(self, plan, entries) -> None:
+        """One line per step on stderr: what ran, the pool, and the device time of the step before."""
+        last = ""
+        if self._trace_events is not None:
+            n, a, b = self._trace_events
+            if b.query():
+                last = f"; step {n} took {a.elapsed_time(b):.3f} ms on the device"
+        prompt = sum(len(e.tokens) for e in entries if len(e.tokens) > 1)
+        decode = sum(1 for e in entries if len(e.tokens) == 1)
+        mgr = self.lm.manager
+        pools = ",".join(f"{mgr.num_free_pages(g)}/{mgr.num_usable_pages(g)}" for g in range(len(mgr.groups)))
+        print(f"[trace] step {self.num_steps}: {len(entries)} requests, {prompt} prompt tokens, {decode} decode tokens, "
+              f"{sum(1 for e in entries if e.want)} sampled; waiting {self.scheduler.num_waiting}, running "
+              f"{self.scheduler.num_running}, preempted {len(plan.preempted)}, ignored {len(plan.ignored)}; free pages {pools}"
+              f"{last}", file=sys.stderr, flush=True)
+
+    def stats(self) -> dict:
+        """Counters of the engine so far (the reference keeps such figures in its metrics registry,
+        backends/vllm/src/llm_engine.rs:314-318)."""
+        mgr = self.lm.manager
+        return {"steps": self.num_steps, "generated_tokens": self.num_generated, "graph_replays": self.lm.step.graph_replays,
+                "preemptions": self.scheduler.num_preemptions, "device_errors": self.num_device_errors,
+                "waiting": self.scheduler.num_waiting, "running": self.scheduler.num_running,
+                "free_pages": [mgr.num_free_pages(g) for g in range(len(mgr.groups))],
+                "usable_pages": [mgr.num_usable_pages(g) for g in range(len(mgr.groups))],
+                "kernel_launches": getattr(self.lm.rt.ops, "launches", 0)}
+
     # ------------------------------------------------------------------ one step
     def step(self) -> List[RequestOutput]:
         """Plans and launches one step, then reads the tokens of the step before it; returns the
@@ -143,7 +183,8 @@ class Engine:
         the model length) act at once.  Requests with a repetition penalty need their history on
         the host, so steps that sample for one are read back before the next is launched.
         """
-        plan = self.scheduler.schedule()
+        with self._range("plan"):
+            plan = self.scheduler.schedule()
         now = time.time()
         finished: List[RequestOutput] = []
         for req in plan.ignored:
@@ -181,7 +222,17 @@ class Engine:
         if not entries:
             self.scheduler.step_done()
             return finished
-        logits = self.lm.step.run(entries)
+        if self.trace:
+            self._trace_step(plan, entries)
+        timed = self.trace and torch.cuda.is_available() and self.lm.rt.device.type == "cuda"
+        if timed:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+        with self._range("launch"):
+            logits = self.lm.step.run(entries)
+        if timed:
+            b.record()
+            self._trace_events = (self.num_steps, a, b)
         self.scheduler.step_done()
         self.num_steps += 1
         previous, self._inflight = self._inflight, None

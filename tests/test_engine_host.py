@@ -122,3 +122,19 @@ def test_step_function_refuses_token_ids_outside_the_vocabulary(tiny_models):
     assert torch.equal(a, b)
     with pytest.raises(ValueError, match="token ids"):
         step.run([StepEntry(8, [-1 - (mgr.state_slot(8) + 1)], [0])])  # another request's slot
+
+
+def test_trace_lines_and_counters(tiny_models, capsys, monkeypatch):
+    """ATOMA_INFER_TRACE=1: one line per step with the batch's composition; ``stats()`` counts what happened."""
+    from atoma_infer_b200.sampling import SamplingParams
+
+    monkeypatch.setenv("ATOMA_INFER_TRACE", "1")
+    d, cfg, page = tiny_models["A"]
+    eng = _engine(d, page, max_num_batched_tokens=8)
+    eng.generate([[1, 2, 3, 4, 5, 6, 7, 8, 9, 10, 11], [5, 6, 7, 8, 9, 10, 11, 12, 13]], SamplingParams(do_sample=False, max_new_tokens=3, ignore_eos_token=True))
+    lines = [l for l in capsys.readouterr().err.splitlines() if l.startswith("[trace] step")]
+    assert len(lines) == eng.num_steps and "8 prompt tokens, 0 decode tokens" in lines[0]
+    assert any("4 prompt tokens, 1 decode tokens" in l for l in lines)  # a portion of the second prompt beside a decode token
+    st = eng.stats()
+    assert st["generated_tokens"] == 6 and st["steps"] == eng.num_steps and st["running"] == 0
+    assert st["free_pages"] == st["usable_pages"]
