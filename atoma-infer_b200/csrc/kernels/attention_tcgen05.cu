@@ -7,15 +7,17 @@
 //     the paged cache into two-stage shared-memory rings; the page ids come from the block table
 //     in shared memory;
 //   * an MMA warp (one elected thread): S = Q K^T is one tcgen05.mma chain (M = 128, N = 128,
-//     K = head size) into one of two tensor-memory buffers; O_tile = P V is a second chain whose A
-//     operand P is read from tensor memory and whose B operand V is read MN-major from shared
-//     memory (no transpose copy);
+//     K = head size) into tensor memory; O += P V is a second chain whose A operand P is read from
+//     tensor memory and whose B operand V is read MN-major from shared memory (no transpose copy); O
+//     stays in tensor memory from the first tile to the last;
 //   * eight softmax warps, two threads per query row: a thread reads its half row of S from tensor
-//     memory, masks by position, keeps the running max and sum (float32, base 2), writes P as
-//     packed bfloat16 back into tensor memory over the scores it has consumed, and adds its half
-//     of the previous tile's O_tile into its float32 output registers with the softmax correction.
-// So the tensor core computes the next tile's scores and the last tile's P V while the softmax of
-// the current tile runs, and the copies run two tiles ahead.  Two blocks fit a multiprocessor for
+//     memory once (64 registers; the scores' columns are then free for the next tile's Q K^T), masks
+//     by position, finds the row maximum with its partner, and writes P as packed bfloat16 into
+//     tensor memory.  The base of the exponentials follows the maximum lazily: while the maximum
+//     grows by less than 2^8 the old base stays, so O (in tensor memory) and the row sum are scaled
+//     down only now and then, by the softmax threads, between two P V products.
+// So the tensor core computes the next tile's scores while the exponentials of the current tile run,
+// and the copies run two tiles ahead.  Two blocks fit a multiprocessor for
 // head size 64; the softmax warps then take registers that the other two warps give up.
 // A portion of a prompt that starts inside a cached context attends to all of it.
 //
@@ -44,15 +46,14 @@ constexpr int BQ = 128;            // query rows per block
 constexpr int BKV = 128;           // keys per tile
 constexpr int HALVES = D / 64;     // 64-column (128-byte) halves of a head
 constexpr int HALF_BYTES = 128 * 128;  // a [128 rows x 64 columns] bfloat16 sub-tile
-// Tensor memory: two buffers.  A buffer holds a tile's scores S (128 columns of float32).  P (128 keys as
-// packed bfloat16: 64 columns) goes over them as the softmax reads them: keys 0..63 into columns 0..31
-// and keys 64..127 into columns 96..127, so that each of a row's two threads overwrites its own scores
-// only.  The tile's P V product takes the columns from O_COL on: between the halves of P for head
-// size 64, behind the scores for 128.
-constexpr uint32_t P_HI_COL = 96;
-constexpr uint32_t O_COL = D == 64 ? 32 : 128;
-constexpr uint32_t BUF_COLS = D == 64 ? 128 : 256;
-constexpr uint32_t TMEM_COLS = 2 * BUF_COLS;
+// Tensor memory of a block: the scores S of one tile (128 columns of float32), P (the tile's 128 keys as packed
+// bfloat16, 64 columns) and the output accumulator O (head size columns of float32), which stays there for the whole
+// key loop: P V of every tile is added to it by the tensor core itself.
+constexpr uint32_t S_COL = 0, P_COL = 128, O_COL = 192;
+constexpr uint32_t TMEM_COLS = D == 64 ? 256 : 512;
+// The exponentials of a row use one base until the row's maximum has grown by more than this (in powers of two):
+// only then are O and the row's sum scaled down.  P then stays below 2^8, far inside the range of bfloat16.
+constexpr float RESCALE_STEP = 8.f;
 constexpr int SOFTMAX_THREADS = 256, SOFTMAX_WARPS = 8;
 constexpr int COPY_WARP = 8, MMA_WARP = 9;
 constexpr int TC_THREADS = 384;  // three warpgroups: two of softmax warps, one with the copy and the MMA warp
@@ -126,24 +127,31 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // Registers move between warpgroups: the copy/MMA warpgroup gives up what the softmax warpgroups take.
 template <int N> __device__ __forceinline__ void regs_release() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 template <int N> __device__ __forceinline__ void regs_take() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n\ttcgen05.wait::ld.sync.aligned;"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
 #pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
-    uint32_t r[8];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+// 64 columns in two loads of 32 and one wait
+__device__ __forceinline__ void tmem_ld32x2(uint32_t taddr, float (&v)[64]) {
+    uint32_t r[64];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%64];\n\t"
+                 "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%65];\n\t"
+                 "tcgen05.wait::ld.sync.aligned;"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+                 : "r"(taddr), "r"(taddr + 32) : "memory");
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+}
+// 32 columns of this thread's lane, written from 32 float registers
+__device__ __forceinline__ void tmem_st32f(uint32_t taddr, const float (&v)[32]) {
+    uint32_t r[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(v[i]);
+    tmem_st32(taddr, r);
 }
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -184,9 +192,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     unsigned char* k_s = q_s + STAGE;       // two stages
     unsigned char* v_s = k_s + 2 * STAGE;   // two stages
     uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * STAGE);
-    // each [2]: K / V stage filled by TMA; scores / P V product of a buffer complete (tensor core);
-    // P of a buffer written / O_tile of a buffer read (softmax warps)
-    uint64_t *k_full = bars, *v_full = bars + 2, *s_done = bars + 4, *o_done = bars + 6, *p_ready = bars + 8, *o_read = bars + 10;
+    // k_full, v_full [2]: a K / V stage filled by TMA.  s_done, pv_done [2, by tile parity]: the scores / the P V
+    // product of a tile complete (tensor core); they also free the tile's K / V stage.  s_free: every softmax warp has
+    // the tile's scores in registers (the next Q K^T may overwrite them).  p_ready: every softmax warp has stored its
+    // part of P (and scaled O if it had to).
+    uint64_t *k_full = bars, *v_full = bars + 2, *s_done = bars + 4, *pv_done = bars + 6, *s_free = bars + 8, *p_ready = bars + 9;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* row_max = reinterpret_cast<float*>(tmem_slot + 2);  // [2 sets][2 halves][128 rows]
@@ -226,7 +236,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
     }
     if (tid == 0) {
         for (int i = 0; i < 8; ++i) mbar_init(&bars[i], 1);
-        for (int i = 8; i < 12; ++i) mbar_init(&bars[i], SOFTMAX_WARPS);  // one arrival per softmax warp
+        for (int i = 8; i < 10; ++i) mbar_init(&bars[i], SOFTMAX_WARPS);  // one arrival per softmax warp
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -286,7 +296,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
                 if (!ok) break;
                 issue_loads(t + 2, 0, k_s + b * STAGE, &k_full[b]);
                 last_k[b] = t + 2;
-                ok = mbar_wait(&o_done[b], par, status, abort_flag);  // P V of tile t is done: its V stage is free
+                ok = mbar_wait(&pv_done[b], par, status, abort_flag);  // P V of tile t is done: its V stage is free
                 if (!ok) break;
                 issue_loads(t + 2, 1, v_s + b * STAGE, &v_full[b]);
                 last_v[b] = t + 2;
@@ -304,7 +314,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
             // ------------------------------------------------------------------ the tensor core's instruction stream
             constexpr uint32_t idesc_s = make_idesc(BQ, BKV, false), idesc_o = make_idesc(BQ, D, true);
             bool ok = true;
-            auto issue_scores = [&](int t) {  // S(t) = Q K(t)^T into buffer t & 1
+            auto issue_scores = [&](int t) {  // S(t) = Q K(t)^T
                 const int b = t & 1;
                 ok = mbar_wait(&k_full[b], (uint32_t)(t >> 1) & 1u, status, abort_flag);
                 if (!ok) return;
@@ -312,25 +322,23 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
 #pragma unroll
                 for (int kd = 0; kd < D / 16; ++kd) {
                     uint32_t off = (kd / 4) * HALF_BYTES + (kd % 4) * 32;
-                    umma_bf16(tmem_base + b * BUF_COLS, make_desc(smem_u32(q_s) + off, 0),
+                    umma_bf16(tmem_base + S_COL, make_desc(smem_u32(q_s) + off, 0),
                               make_desc(smem_u32(k_s) + b * STAGE + off, 0), idesc_s, kd > 0);
                 }
                 umma_commit(&s_done[b]);
             };
             issue_scores(0);
-            if (ok && ntiles > 1) issue_scores(1);  // both buffers are free at the start
             for (int t = 0; t < ntiles && ok; ++t) {
                 const int b = t & 1;
                 const uint32_t par = (uint32_t)(t >> 1) & 1u;
-                if (t >= 1 && t + 1 < ntiles) {
-                    // the other buffer: the softmax warps take its last product (tile t - 1) in the middle of
-                    // this tile's softmax; then the scores of tile t + 1 may overwrite it
-                    ok = mbar_wait(&o_read[b ^ 1], (uint32_t)((t - 1) >> 1) & 1u, status, abort_flag);
+                if (t + 1 < ntiles) {
+                    // the softmax warps hold the scores of tile t in registers: the next tile's may take their place
+                    ok = mbar_wait(s_free, (uint32_t)t & 1u, status, abort_flag);
                     if (!ok) break;
                     issue_scores(t + 1);
                     if (!ok) break;
                 }
-                ok = mbar_wait(&p_ready[b], par, status, abort_flag);  // P(t) is in tensor memory, V(t) is whole
+                ok = mbar_wait(p_ready, (uint32_t)t & 1u, status, abort_flag);  // P(t) is in tensor memory, O is scaled
                 if (!ok) break;
                 ok = mbar_wait(&v_full[b], par, status, abort_flag);
                 if (!ok) break;
@@ -338,10 +346,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
 #pragma unroll
                 for (int ks = 0; ks < BKV / 16; ++ks) {
                     uint64_t bd = make_desc(smem_u32(v_s) + b * STAGE + ks * 16 * 128, HALF_BYTES);
-                    umma_bf16_a_tmem(tmem_base + b * BUF_COLS + O_COL, tmem_base + b * BUF_COLS + (ks < 4 ? ks * 8 : P_HI_COL + (ks - 4) * 8), bd,
-                                     idesc_o, ks > 0);
+                    umma_bf16_a_tmem(tmem_base + O_COL, tmem_base + P_COL + ks * 8, bd, idesc_o, (t > 0 || ks > 0) ? 1u : 0u);
                 }
-                umma_commit(&o_done[b]);
+                umma_commit(&pv_done[b]);
             }
         }
     } else {
@@ -349,29 +356,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
         if (D == 64) regs_take<104>();
         const uint32_t tmem_row = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);  // a warp reaches the lanes of its quarter
         constexpr int DH = D / 2;  // my half of the head
-        float m_run = -INFINITY, l_run = 0.f;  // l_run: the sum over my half of the keys only (the halves add up at the end)
-        float corr_prev = 1.f;                 // the correction that belongs to the product not yet added
-        float o[DH];
-#pragma unroll
-        for (int i = 0; i < DH; ++i) o[i] = 0.f;
+        // m_run: the row's maximum so far; m_base: the base of the exponentials, which follows it lazily;
+        // l_run: the sum over my half of the keys, in units of 2^m_base (the halves add up at the end)
+        float m_run = -INFINITY, m_base = -INFINITY, l_run = 0.f;
         bool ok = true;
-        // o = o * correction + my half row of P V of tile u, eight columns at a time (few registers: it
-        // runs in the middle of a softmax); then the buffer is free for the scores of tile u + 2
-        auto add_product = [&](int u) {
-            const int b = u & 1;
-            if (!mbar_wait(&o_done[b], (uint32_t)(u >> 1) & 1u, status, abort_flag)) ok = false;
-            tc_fence_after();
-#pragma unroll
-            for (int ch = 0; ch < DH / 8; ++ch) {
-                float v[8];
-                tmem_ld8(tmem_row + b * BUF_COLS + O_COL + half * DH + ch * 8, v);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) o[ch * 8 + i] = o[ch * 8 + i] * corr_prev + v[i];
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&o_read[b]);
-        };
 
         // After a timeout anywhere in the block every wait returns at once and `ok` stays false, but the
         // loop still runs all its tiles: the two threads of a row meet at their barrier once per tile,
@@ -380,65 +368,68 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
             const int k0 = k_first + t * BKV;
             const int b = t & 1;
             const uint32_t par = (uint32_t)(t >> 1) & 1u;
-            const uint32_t tmem_buf = tmem_row + b * BUF_COLS;
             if (!mbar_wait(&s_done[b], par, status, abort_flag)) ok = false;
             tc_fence_after();
-
-            // ---- softmax of my half row, in two passes over its 64 scores in tensor memory (16 at a time, so
-            // that few registers are live): first the maximum, then the exponentials
+            // ---- my half row of the scores, once, into registers; then the scores' columns are free
+            float v[64];
+            tmem_ld32x2(tmem_row + S_COL + half * 64, v);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_free);
             const bool need_mask = window > 0 || k0 + BKV - 1 > p_first || k0 < kbeg || nt < TPT;  // same for the whole block
-            auto load_scores = [&](int c, float (&v)[16]) {  // unscaled: the scale goes into the exponent's FMA
-                tmem_ld16(tmem_buf + half * 64 + c * 16, v);
-                if (need_mask) {
+            if (need_mask) {
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        int key = k0 + half * 64 + c * 16 + i;
-                        bool vis = key <= my_pos && (window <= 0 || my_pos - key < window);
-                        v[i] = vis ? v[i] : -INFINITY;
-                    }
+                for (int i = 0; i < 64; ++i) {
+                    int key = k0 + half * 64 + i;
+                    bool vis = key <= my_pos && (window <= 0 || my_pos - key < window);
+                    v[i] = vis ? v[i] : -INFINITY;
                 }
-            };
+            }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float v[16];
-                load_scores(c, v);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
-            }
+            for (int i = 0; i < 64; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], v[i]);
             // the row's maximum: the two threads of a row (warps w and w + 4) swap their halves' maxima through
             // shared memory and meet at a barrier of their own, 64 threads wide
             float* slot = row_max + (t & 1) * 2 * BQ;  // two sets, so that a fast pair cannot overwrite a slow reader's value
             slot[half * BQ + row] = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");
             const float mx = fmaxf(slot[row], slot[BQ + row]) * scale_log2;  // scale > 0: the max commutes with it
-            const float m_new = fmaxf(m_run, mx);
-            const float base = m_new == -INFINITY ? 0.f : m_new;
-            const float corr = fast_exp2(m_run - base);
+            m_run = fmaxf(m_run, mx);
+            // The base moves only when the maximum has outgrown it by more than RESCALE_STEP (or at the first key
+            // the row sees): both threads of a row decide alike, they hold the same numbers.
+            const bool rebase = m_run > m_base + RESCALE_STEP || (m_base == -INFINITY && m_run > -INFINITY);
+            const float corr = rebase ? fast_exp2(m_base - m_run) : 1.f;  // 0 for the first base
+            if (rebase) m_base = m_run;
+            const float base = m_base == -INFINITY ? 0.f : m_base;
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
             uint32_t pk[32];  // my 64 keys of P, two to a column
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float v[16];
-                load_scores(c, v);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    float p0 = fast_exp2(fmaf(v[2 * i], scale_log2, -base));
-                    float p1 = fast_exp2(fmaf(v[2 * i + 1], scale_log2, -base));
-                    __nv_bfloat162 two = __floats2bfloat162_rn(p0, p1);  // .x = p0 in the low half: the lower key
-                    sum4[i & 3] += p0 + p1;
-                    pk[c * 8 + i] = *reinterpret_cast<uint32_t*>(&two);
-                }
-                // ---- in between, the product of the tile before this one: the tensor core made it while this
-                // tile's maximum was found, and once it is taken the scores of the next tile can start early
-                if (c == 1 && t >= 1) add_product(t - 1);
+            for (int i = 0; i < 32; ++i) {
+                float p0 = fast_exp2(fmaf(v[2 * i], scale_log2, -base));
+                float p1 = fast_exp2(fmaf(v[2 * i + 1], scale_log2, -base));
+                __nv_bfloat162 two = __floats2bfloat162_rn(p0, p1);  // .x = p0 in the low half: the lower key
+                sum4[i & 3] += p0 + p1;
+                pk[i] = *reinterpret_cast<uint32_t*>(&two);
             }
-            // P goes over my own scores only (my partner may still be reading theirs): the first half row's
-            // keys into columns 0..31, the second's into 96..127; the product lands between them
-            tmem_st32(tmem_buf + half * 96, pk);
             l_run = l_run * corr + (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-            m_run = m_new;
-            corr_prev = corr;
+            // ---- the product of the tile before must be complete before P is overwritten and before O is touched
+            if (t >= 1) {
+                if (!mbar_wait(&pv_done[b ^ 1], (uint32_t)((t - 1) >> 1) & 1u, status, abort_flag)) ok = false;
+                tc_fence_after();
+                // O (my half of the row) times the correction, if any row of this warp moved its base
+                // (the loads and stores of tensor memory are warp-wide)
+                if (__any_sync(0xffffffffu, rebase)) {
+#pragma unroll
+                    for (int ch = 0; ch < DH / 32; ++ch) {
+                        float o[32];
+                        tmem_ld32(tmem_row + O_COL + half * DH + ch * 32, o);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) o[i] *= corr;
+                        tmem_st32f(tmem_row + O_COL + half * DH + ch * 32, o);
+                    }
+                }
+            }
+            tmem_st32(tmem_row + P_COL + half * 32, pk);
 
             // ---- V rows that no page delivered, or that lie beyond the last key, must be zero (0 * NaN would
             // poison P V): the last tile, a tile that starts before the window, a block table with holes
@@ -457,28 +448,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const bf16* _
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_ready[b]);
+            if (lane == 0) mbar_arrive(p_ready);
         }
-        if (ntiles > 0) add_product(ntiles - 1);
+        if (ntiles > 0) {
+            if (!mbar_wait(&pv_done[(ntiles - 1) & 1], (uint32_t)((ntiles - 1) >> 1) & 1u, status, abort_flag)) ok = false;
+            tc_fence_after();
+        }
 
-        // the two halves of a row saw the same maxima, so their sums simply add; the set of slots that
+        // the two halves of a row used the same bases, so their sums simply add; the set of slots that
         // the next tile would have used is free (the pair has met since anybody read it)
         float* slot = row_max + (ntiles & 1) * 2 * BQ;
         slot[half * BQ + row] = l_run;
         asm volatile("bar.sync %0, 64;" ::"r"(1 + (warp & 3)) : "memory");
-        if (ok && my_valid) {
-            const float l_all = slot[row] + slot[BQ + row];
-            const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-            bf16* dst = out + ((size_t)(row0 + t0 + my_tok) * nq + kvh * G + my_hd) * D + half * DH;
+        const float l_all = slot[row] + slot[BQ + row];
+        const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+        bf16* dst = out + ((size_t)(row0 + t0 + my_tok) * nq + kvh * G + my_hd) * D + half * DH;
 #pragma unroll
-            for (int c = 0; c < DH / 8; ++c) {
-                uint32_t w[4];
+        for (int ch = 0; ch < DH / 32; ++ch) {
+            float o[32];
+            if (ntiles > 0) tmem_ld32(tmem_row + O_COL + half * DH + ch * 32, o);  // warp-wide: every lane takes part
+            if (ok && my_valid) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    __nv_bfloat162 two = __floats2bfloat162_rn(o[c * 8 + 2 * i] * inv, o[c * 8 + 2 * i + 1] * inv);
-                    w[i] = *reinterpret_cast<uint32_t*>(&two);
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        __nv_bfloat162 two = __floats2bfloat162_rn(o[c * 8 + 2 * i] * inv, o[c * 8 + 2 * i + 1] * inv);
+                        w[i] = *reinterpret_cast<uint32_t*>(&two);
+                    }
+                    *reinterpret_cast<uint4*>(dst + ch * 32 + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
-                *reinterpret_cast<uint4*>(dst + c * 8) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
     }
