@@ -29,7 +29,15 @@ def run_attention(rt, entries, nq, nkv, d, page_size, window=None, seed=0, scale
     qs = [torch.randn(L, nq, d, generator=g) for L in lengths]
     ks = [torch.randn(L, nkv, d, generator=g) for L in lengths]
     vs = [torch.randn(L, nkv, d, generator=g) for L in lengths]
-    if stand_out is not None:  # one far key that the last query must find among all the others
+    if isinstance(stand_out, tuple):  # ("plateau", far): see test_prefill_where_a_late_key_outgrows_the_base
+        far = stand_out[1]
+        for q, k in zip(qs, ks):
+            u = torch.randn(nkv, d, generator=g)
+            u = u / u.norm(dim=-1, keepdim=True) * math.sqrt(d)
+            k[:far] = u + 0.1 * k[:far]
+            k[far] = 1.75 * u
+            q[-1] = u.repeat_interleave(nq // nkv, dim=0)
+    elif stand_out is not None:  # one far key that the last query must find among all the others
         for q, k in zip(qs, ks):
             k[stand_out] *= 4.0
             q[-1] = k[stand_out].repeat_interleave(nq // nkv, dim=0) * 1.5
@@ -80,6 +88,23 @@ def test_prefill_with_cached_context_bf16(rts, d, nq, nkv, page):
     entries = [(0, 70), (37, 29), (130, 2), (64, 1), (5, 131)]
     got, want = run_attention(rts["bfloat16"], entries, nq, nkv, d, page, seed=d)
     assert worst(got, want) < 2e-2  # values are O(1); bfloat16 P and outputs
+
+
+@pytest.mark.parametrize("d,nq,nkv,page", [(64, 8, 2, 16), (128, 6, 2, 16), (64, 3, 1, 8)])
+def test_prefill_where_a_late_key_outgrows_the_base(rts, d, nq, nkv, page):
+    """The tcgen05 kernel keeps the output in tensor memory and moves the base of its exponentials only when a
+    row's maximum has grown by more than 2^8; then it scales the output there.  Here the last query of each request
+    meets, in its third and later key tiles, a key whose score towers over everything before it (and, in the
+    second request, a second such key further on), so the scaling runs, more than once, at a page's and a tile's edge."""
+    rt = rts["bfloat16"]
+    for entries, far in (([(0, 450)], 300), ([(130, 390)], 383), ([(0, 1100)], 1023)):
+        got, want = run_attention(rt, entries, nq, nkv, d, page, seed=far, stand_out=far, scale=1.0)
+        assert worst(got, want) < 3e-2, (entries, far)
+        # a plateau of equal scores and then one key 2^8.7 (head size 64) above it: the hundreds of keys before it
+        # still carry as much weight together as the one, so a wrong scaling of what was summed before would show
+        got, want = run_attention(rt, entries, nq, nkv, d, page, seed=far, stand_out=("plateau", far))
+        assert worst(got, want) < 3e-2, (entries, far, "plateau")
+        assert float(want[-1][-1].abs().max()) > 0.05
 
 
 @pytest.mark.parametrize("cluster", [True, False])
