@@ -12,10 +12,14 @@ import ctypes
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
+import numpy as np
+
 from ..csrc.build import host_library
 from .spec import FULL_KEYS, WINDOW_KEYS, CacheGroup, CacheNeed
 
 _ERRORS = {
+    -20: "an entry brings no tokens", -21: "a request appears twice in one step",
+    -22: "a wanted place lies outside the entry's tokens", -23: "token ids must lie in the vocabulary",
     -1: "out of pages", -2: "no free state slot", -3: "unknown request (or freed twice)",
     -4: "request already exists", -5: "advance beyond what was reserved",
     -6: "the request would not fit an empty cache", -7: "bad argument",
@@ -56,6 +60,9 @@ def _bind(lib):
         "cm_num_free_slots": (c.c_int, [c.c_void_p]),
         "cm_num_requests": (c.c_int, [c.c_void_p]),
         "cm_audit": (c.c_int, [c.c_void_p, c.c_char_p, c.c_int]),
+        # arrays go as addresses (numpy's .ctypes.data)
+        "cm_step_begin": (c.c_int, [c.c_void_p, c.c_int] + [c.c_void_p] * 5 + [c.c_int] + [c.c_void_p] * 5),
+        "cm_step_fill": (None, [c.c_void_p, c.c_int] + [c.c_void_p] * 8 + [c.c_int] * 11 + [c.c_void_p] * 2 + [c.c_int] * 5),
         "sched_create": (c.c_void_p, [c.c_void_p, c.c_int, c.c_int, i64, c.c_int]),
         "sched_destroy": (None, [c.c_void_p]),
         "sched_add_request": (c.c_int, [c.c_void_p, i64, i64]),
@@ -150,6 +157,32 @@ class CacheManager:
     def table_into(self, req: int, group: int, address: int, cap: int) -> int:
         """Writes the block table to int32 memory at ``address``; returns its full length."""
         return self._check(self._lib.cm_table(self._h, req, group, address, cap), f"table({req})")
+
+    def step_begin(self, reqs, ntok, tokens, want_count, wants, vocab: int):
+        """Admits and checks the entries of a step and claims their pages, in one native call.
+        Arguments are numpy arrays: request ids (int64), tokens each entry brings, the tokens
+        themselves one entry after the other, wanted places each entry has, and those places (all
+        int32).  Returns (tokens cached, state slot, starts-now flag) per entry and the longest block
+        table per group.  Raises ValueError for a malformed entry, CacheError/OutOfPages when the
+        cache refuses; the refused entry leaves nothing behind."""
+        n = len(reqs)
+        ctx, slot, new = np.empty(n, np.int64), np.empty(n, np.int32), np.empty(n, np.int32)
+        lens = np.ones(max(len(self.groups), 1), np.int32)
+        bad = ctypes.c_int32(-1)
+        code = self._lib.cm_step_begin(self._h, n, reqs.ctypes.data, ntok.ctypes.data, tokens.ctypes.data,
+                                       want_count.ctypes.data, wants.ctypes.data, vocab, ctx.ctypes.data, slot.ctypes.data,
+                                       new.ctypes.data, lens.ctypes.data, ctypes.addressof(bad))
+        if code <= -20:
+            k = bad.value
+            raise ValueError(f"request {int(reqs[k])} (entry {k} of the step, {int(ntok[k])} tokens): {_ERRORS[code]}"
+                             + (f" [0, {vocab})" if code == -23 else ""))
+        if code < 0:
+            self._check(code, f"step entry {bad.value} (request {int(reqs[bad.value])})")
+        return ctx, slot, new, lens
+
+    def step_fill(self, *args) -> None:
+        """Writes the step's metadata buffer (csrc/host/step_meta.cpp gives the arguments)."""
+        self._lib.cm_step_fill(self._h, *args)
 
     def table_len(self, req: int, group: int = 0) -> int:
         return self._check(self._lib.cm_table_len(self._h, req, group), f"table_len({req})")

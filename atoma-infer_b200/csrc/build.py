@@ -126,7 +126,7 @@ def load_library(name: str, sources: Sequence[str], *, cuda: bool, defines: Opti
     return lib
 
 
-HOST_SOURCES = ["host/capi.cpp", "host/cache_manager.cpp", "host/scheduler.cpp"]
+HOST_SOURCES = ["host/capi.cpp", "host/cache_manager.cpp", "host/scheduler.cpp", "host/step_meta.cpp"]
 
 
 def host_library() -> ctypes.CDLL:

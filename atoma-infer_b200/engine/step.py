@@ -90,71 +90,32 @@ class StepFunction:
         """Claims pages, builds the metadata on the host.  Returns (host buffer, layout, infos, R).
         ``pad_to``: lay the arrays out for that many tokens, entries and rows (a captured graph's
         fixed sizes); the header still holds the true counts, which is what the kernels obey."""
-        mgr, ps = self.manager, self.page_size
-        vocab = self.model.spec.vocab_size
-        infos: List[EntryInfo] = []
-        seen = set()
-        start = 0
-        for e in entries:
-            n = len(e.tokens)
-            if n == 0:
-                raise ValueError(f"request {e.req} brings no tokens")
-            if e.req in seen:
-                raise ValueError(f"request {e.req} appears twice in one step")
-            seen.add(e.req)
-            added = not mgr.has_request(e.req)
-            slot = mgr.add_request(e.req) if added else mgr.state_slot(e.req)
-            ctx_len = mgr.num_tokens(e.req)
-            is_new = ctx_len == 0  # also a request that a scheduler admitted (again) and that has run nothing yet
-            try:
-                for w in e.want:
-                    if not (0 <= w < n):
-                        raise ValueError(f"request {e.req}: wanted place {w} is outside its {n} tokens")
-                # token ids: in the vocabulary, or the one negative id that means "the token the sampler
-                # left on the device for this request's slot" (a single decode token)
-                lo, hi = min(e.tokens), max(e.tokens)
-                if hi >= vocab or (lo < 0 and not (n == 1 and ctx_len > 0 and lo == -1 - slot)):
-                    raise ValueError(f"request {e.req}: token ids must lie in [0, {vocab})")
-                mgr.reserve(e.req, ctx_len + n)
-            except Exception:
-                if added:
-                    mgr.free_request(e.req)
-                raise
-            infos.append(EntryInfo(e.req, start, n, ctx_len, slot, is_new))
-            start += n
-        T, S = start, len(infos)
-        R = sum(len(e.want) for e in entries)
-        strides = tuple(max((mgr.table_len(i.req, g) for i in infos), default=1) for g in range(len(mgr.groups)))
+        mgr = self.manager
+        S = len(entries)
+        counts = [len(e.tokens) for e in entries]
+        ntok = np.asarray(counts, dtype=np.int32)
+        reqs = np.asarray([e.req for e in entries], dtype=np.int64)
+        tokens = np.fromiter((t for e in entries for t in e.tokens), dtype=np.int64, count=sum(counts))
+        if tokens.size and (tokens.max() > 0x7FFFFFFF or tokens.min() < -0x80000000):
+            raise ValueError("token ids must fit 32 bits")
+        tokens = tokens.astype(np.int32)
+        want_count = np.asarray([len(e.want) for e in entries], dtype=np.int32)
+        wants = np.fromiter((w for e in entries for w in e.want), dtype=np.int32, count=int(want_count.sum()))
+        ctx, slots, new, strides = mgr.step_begin(reqs, ntok, tokens, want_count, wants, self.model.spec.vocab_size)
+        starts = np.cumsum(ntok) - ntok
+        infos = [EntryInfo(e.req, int(a), int(n), int(c), int(s), bool(f))
+                 for e, a, n, c, s, f in zip(entries, starts, ntok, ctx, slots, new)]
+        T, R = int(tokens.size), int(wants.size)
+        strides = tuple(int(x) for x in strides[:len(mgr.groups)])
         lay = MetaLayout(max(T, pad_to), max(S, pad_to), max(R, pad_to), strides)
         host = self._host_buffer(lay.size)
-        h = host.numpy()
-        h[:META_HEADER_INTS] = 0
-        h[META_NUM_TOKENS], h[META_NUM_ENTRIES], h[META_NUM_ROWS] = T, S, R
-        rows = []
-        for k, (e, i) in enumerate(zip(entries, infos)):
-            a, b = i.start, i.start + i.num_tokens
-            h[lay.tokens + a:lay.tokens + b] = np.asarray(e.tokens, dtype=np.int64)
-            h[lay.positions + a:lay.positions + b] = np.arange(i.context_len, i.context_len + i.num_tokens)
-            h[lay.token_entry + a:lay.token_entry + b] = k
-            h[lay.cu + k] = a
-            h[lay.ctx + k] = i.context_len
-            h[lay.slots + k] = i.state_slot
-            rows += [a + w for w in e.want]
-        h[lay.cu + S:lay.cu + lay.S + 1] = T
-        h[lay.tokens + T:lay.tokens + lay.T] = 0
-        h[lay.positions + T:lay.positions + lay.T] = 0
-        h[lay.token_entry + T:lay.token_entry + lay.T] = 0
-        h[lay.ctx + S:lay.ctx + lay.S] = 0
-        h[lay.slots + S:lay.slots + lay.S] = 0
-        h[lay.rows:lay.rows + max(lay.R, 1)] = 0
-        if rows:
-            h[lay.rows:lay.rows + R] = rows
-        base = h.ctypes.data
-        for g, (off, stride) in enumerate(zip(lay.tables, strides)):
-            h[META_BT_STRIDE + g], h[META_BT_OFFSET + g] = stride, off
-            h[off:off + lay.S * stride] = -1
-            for k, i in enumerate(infos):
-                mgr.table_into(i.req, g, base + 4 * (off + k * stride), stride)
+        table_off = np.asarray(lay.tables or [0], dtype=np.int32)
+        table_stride = np.asarray(strides or (1,), dtype=np.int32)
+        mgr.step_fill(S, reqs.ctypes.data, ntok.ctypes.data, ctx.ctypes.data, slots.ctypes.data, tokens.ctypes.data,
+                      want_count.ctypes.data, wants.ctypes.data, host.data_ptr(), META_HEADER_INTS, lay.T, lay.S, lay.R,
+                      lay.tokens, lay.positions, lay.token_entry, lay.cu, lay.ctx, lay.slots, lay.rows,
+                      table_off.ctypes.data, table_stride.ctypes.data, META_NUM_TOKENS, META_NUM_ENTRIES, META_NUM_ROWS,
+                      META_BT_STRIDE, META_BT_OFFSET)
         return host, lay, infos, R
 
     def context(self, dev: torch.Tensor, lay: MetaLayout, infos: List[EntryInfo]) -> StepContext:
