@@ -22,7 +22,7 @@
 // Status words (a device int32 array the host reads after a step); non-zero = fault.
 #define STATUS_BAD_TOKEN 0
 #define STATUS_BAD_PAGE 1
-#define STATUS_WORDS 4
+#define STATUS_WORDS 8
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }

@@ -1,0 +1,769 @@
+// A run of decoder layers of a decode step (at most 16 rows) as ONE persistent kernel, specialised by head
+// size (-DHEAD_DIM=...).
+//
+// A decode step's time is the time to read every weight once.  Launched kernel by kernel, the weight stream
+// stops at every kernel boundary: a linear of a few microseconds spends a third of its time starting and
+// draining, and the norms and the attention between the linears read no weights at all.  Here one block per
+// multiprocessor stays resident for all layers, and a warp of its own does nothing but stream the block's share
+// of every weight matrix, in the order the layers use them, through a ring of shared-memory stages (bulk async
+// copies that complete on mbarriers).  The stream depends on nothing the step computes, so it runs ahead of
+// the arithmetic by the depth of the ring: while the blocks wait for each other between two phases, compute a
+// norm, or walk keys and values, the next linears' weights keep arriving.
+//
+// A layer is five phases with a grid-wide barrier after each (the layer of models/src/llama.rs:393-410):
+//   1. RMSNorm of the residual rows (every block computes it for itself, into shared memory), then the fused
+//      q/k/v projection;
+//   2. rotation of q and k, the new key and value written to their page, attention over the cached pages (the
+//      key tiles of all requests dealt out evenly over the blocks, flat_attention in attention_tiles.cuh);
+//   3. output projection, added into the float32 residual;
+//   4. RMSNorm again, gate/up projection with the SwiGLU epilogue;
+//   5. down projection, added into the residual.
+// A linear's 16-row weight tiles (16 output columns) are dealt to the blocks like cards, the deal going on from
+// phase to phase, so over a layer every block streams the same number of bytes, give or take a tile; a block
+// multiplies a whole tile (all of K) itself: its arithmetic warps split each 512-wide stage between them
+// and add up through shared memory in a fixed order, so a result does not depend on timing.  The weights are
+// the A operand of mma.sync m16n8k16 and the rows of x the B operand, as in the stand-alone few-row linear.
+//
+// Every wait is bounded (mbarriers and the grid barrier alike).  A block whose wait runs out raises a status
+// word and an abort flag and from then on waits for nothing: it walks the rest of the schedule (its results
+// are void, the host sees the status word) and keeps counting itself in at the grid barriers, so no other
+// block waits for it in vain, and it leaves only when the copies it issued have landed.
+//
+// The reference launches about 25 kernels a layer through candle (models/src/llama.rs:259-410).
+#include <cuda.h>
+
+#include <cstring>
+
+#include "attention_tiles.cuh"
+
+int g_use_pdl = 1;
+extern "C" void kernels_set_pdl(int mode) { g_use_pdl = mode; }
+
+#define STATUS_STACK_WAIT 4  // a block of this kernel gave up a wait: 1 + block index
+
+namespace {
+
+int g_stack_inflight = 0;            // set through decode_stack_set_inflight (0: ST_INFLIGHT)
+long long* g_stack_times = nullptr;  // set through decode_stack_set_times: where the next launches leave their clocks
+
+// Arithmetic warps.  Eight (two a scheduler, which hides the latencies of a stage's loads and multiply-adds behind
+// each other) where the attention's registers allow it: with the stream warp that is 288 threads and at most 168
+// registers a thread, which the walk over the keys fits into up to head size 64.  Larger heads: four (255 registers).
+// The first four (DEC_WARPS) walk the keys.
+constexpr int ST_WARPS = D <= 64 ? 8 : 4;
+constexpr int ST_KB = 16 / ST_WARPS;           // 32-wide k blocks of a stage per warp
+constexpr int ST_CONSUMERS = ST_WARPS * 32;
+constexpr int ST_THREADS = ST_CONSUMERS + 32;  // and the warp that streams weights
+constexpr int ST_KC = 512;                     // k per ring stage: eight groups of 64
+constexpr int ST_STAGE_BYTES = 16 * ST_KC * 2; // 16 weight rows
+constexpr int ST_MAX_STAGES = 12;
+constexpr int ST_MIN_STAGES = 3;
+// Stages asked for and not yet landed, per block.  What is in flight queues in the memory system ahead of every
+// other read of the GPU, the arithmetic warps' dependent reads (the barrier's counter, queries, block tables) among
+// them; the ring's other stages hold weights that have landed and wait to be used.
+constexpr int ST_INFLIGHT = 6;
+constexpr int ST_MAX_ROWS = 16;
+constexpr int ST_XRING = 8;                    // most slots of the ring of x chunks
+constexpr uint32_t ST_WAIT_POLLS = 1u << 22;   // about a quarter of a second
+constexpr int BAR_CONSUMERS = 1, BAR_ATTENTION = 2, BAR_ALL = 3;
+
+// A layer as the kernel sees it.  The weight matrices are tensor maps: a [N, K] row-major matrix seen as
+// [K / 64][N][64] (the 64 contiguous, 128 bytes), so that one copy brings 16 rows x 512 k (or 8 x 512 for the
+// stacked gate/up matrix: eight gate rows, then the eight up rows that belong to them) into shared memory as eight
+// 128-byte-swizzled blocks of [rows][64], which ldmatrix reads without bank conflicts.
+struct alignas(64) StackLayer {
+    CUtensorMap map_qkv;      // [(nq + 2 nkv) D, H], box of 16 rows
+    CUtensorMap map_o;        // [H, nq D], 16 rows
+    CUtensorMap map_gate_up;  // [2 I, H], 8 rows
+    CUtensorMap map_down;     // [H, I], 16 rows
+    const float* norm1;       // [H]
+    const float* norm2;
+    const float* inv_freq;    // [rot / 2]
+    bf16* cache;              // this layer's pages
+    int store_kv;             // 0: the layer reads another layer's cache and writes nothing
+    int pad[7];
+};
+static_assert(sizeof(StackLayer) % 64 == 0, "descriptors lie back to back on 64-byte boundaries");
+
+struct StackParams {
+    const StackLayer* layers;
+    float* resid;               // [M, H] float32 residual stream, updated in place
+    const bf16* delta;          // optional [M, H]: still to be added to resid (done before the first layer)
+    bf16* qkv;                  // workspace [M, (nq + 2 nkv) D]
+    bf16* attn_out;             // workspace [M, nq D]
+    bf16* act;                  // workspace [M, I]
+    bf16* xw;                   // workspace [M, H]: the residual times the next norm's weight
+    float* ss_part;             // workspace [ceil(H / 16)][16]: shares of the rows' sums of squares
+    float* part_o;              // attention partial results: (blocks + S nkv) G D floats
+    float* part_ml;             // and their (max, sum): (blocks + S nkv) G 2 floats
+    int* counters;              // S nkv ints, zero before and after
+    unsigned long long* arrivals;  // the grid barrier's counter: only ever grows, by the same amount every launch
+    const int* meta;
+    const int* cu_tokens;
+    const int* positions;
+    int* status;
+    int num_layers, group, M, H, I, nq, nkv, rot, window, num_pages, page_size, S, stages, inflight;
+    float eps, scale_log2;
+    long long* times;           // optional [blocks][layers][10]: the clock after every phase and every barrier (measurements)
+};
+
+struct Linear {
+    const CUtensorMap* map;
+    int N, K, epi, tiles;  // epi 0: bfloat16 rows out; 1: silu(gate) * up; 2: added into the residual
+};
+
+__device__ __forceinline__ Linear phase_linear(const StackParams& p, const StackLayer* ly, int phase) {
+    Linear l;
+    if (phase == 0) { l.map = &ly->map_qkv; l.N = (p.nq + 2 * p.nkv) * D; l.K = p.H; l.epi = 0; }
+    else if (phase == 1) { l.map = &ly->map_o; l.N = p.H; l.K = p.nq * D; l.epi = 2; }
+    else if (phase == 2) { l.map = &ly->map_gate_up; l.N = 2 * p.I; l.K = p.H; l.epi = 1; }
+    else { l.map = &ly->map_down; l.N = p.H; l.K = p.I; l.epi = 2; }
+    l.tiles = l.epi == 1 ? (p.I + 7) / 8 : (l.N + 15) / 16;
+    return l;
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// One box of a 3-d tensor map into shared memory; `hint`: an L2 eviction policy (weights are read once a step).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint64_t* bar,
+                                                 uint64_t hint) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)), "l"(hint) : "memory");
+}
+// Before the copy engine reads global memory, or writes shared memory, that threads have written or used in the ordinary way.
+__device__ __forceinline__ void fence_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ unsigned long long ld_acquire(const unsigned long long* p) {
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync %0, %1;" ::"n"(BAR_CONSUMERS), "n"(ST_CONSUMERS) : "memory"); }
+
+// What a block knows about its own failure: once `flag` is set nothing waits any more.
+struct Giveup {
+    volatile int* flag;
+    int* status;
+    int code;
+    __device__ __forceinline__ void raise() const {
+        *flag = 1;
+        atomicCAS(status + STATUS_STACK_WAIT, 0, code);
+    }
+};
+
+// Bounded wait for a phase of a shared-memory barrier.  false: given up (now or earlier).
+__device__ __forceinline__ bool wait_phase(uint64_t* bar, uint32_t parity, const Giveup& gu, bool heed_flag = true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t i = 0; i < ST_WAIT_POLLS; ++i) {
+        if (heed_flag && *gu.flag) return false;
+        if (mbar_try_wait(bar, parity)) return true;
+        if (i > 32) __nanosleep(32);
+    }
+    gu.raise();
+    return false;
+}
+
+__device__ __forceinline__ void stamp(const StackParams& p, int layer, int slot, int tid) {
+    if (p.times && tid == 0) {
+        long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        p.times[((size_t)blockIdx.x * p.num_layers + layer) * 10 + slot] = t;
+    }
+}
+
+// All blocks meet: everything written before it by any block is visible after it to every block.  The block's threads
+// meet first; one of them counts the block in with release semantics (which covers what the others wrote before they
+// met) and polls with acquire semantics; then the threads meet again.
+__device__ __forceinline__ void grid_barrier(const StackParams& p, unsigned long long& target, int tid, const Giveup& gu) {
+    consumer_sync();
+    if (tid == 0) {
+        target += gridDim.x;
+        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(p.arrivals), "l"(1ull) : "memory");
+        if (!*gu.flag) {
+            uint32_t polls = 0;
+            while (ld_acquire(p.arrivals) < target) {
+                if (++polls > ST_WAIT_POLLS || *gu.flag) { gu.raise(); break; }
+                if (polls > 4096) __nanosleep(64);
+            }
+        }
+    }
+    consumer_sync();
+}
+
+// What a block keeps in shared memory.  Ring, region and the slots of the x ring start on 1,024-byte boundaries (the
+// swizzle of a 128-byte row is a function of address bits 7 to 9).
+struct BlockMem {
+    uint32_t ring;         // weight stages (shared-window addresses)
+    uint32_t region;       // rows of x for a linear, as [K / 64][rows][64] swizzled; or a ring of x chunks (eight groups
+                           // of 64 each); or the attention's query tile and key/value stages
+    uint64_t* full;        // [ST_MAX_STAGES] a stage has landed
+    uint64_t* empty;       // [ST_MAX_STAGES] the arithmetic warps are done with a stage
+    int xdepth;            // slots of the x ring
+    uint64_t* xbar;        // the rows of x have landed
+    uint64_t* xfull;       // [ST_XRING] a chunk of x has landed
+    uint64_t* xempty;      // [ST_XRING]
+    float* redbuf;         // two reduction buffers
+    float* inv;            // [16] 1 / rms of the rows
+};
+
+// Where a block stands in its rings.
+struct RingCursor {
+    unsigned slot, parity;      // the weight stage that comes next and the parity of its "landed" phase
+    unsigned deal;              // tiles dealt so far, over all phases
+    unsigned tiles;             // tiles this block has finished (picks the reduction buffer)
+    unsigned xslot, xparity;    // the same for the ring of x chunks
+    unsigned xissue, xiparity;  // thread 0: the slot its next chunk of x goes to, and the parity of that slot's "free" phase
+    unsigned xuse;              // parity of the next "rows of x have landed"
+};
+
+// All rows of x (a [M, width] bfloat16 matrix under `map`, boxes of `rows` rows) into the region; every arithmetic
+// thread returns when they have landed.  The caller has made sure nobody still uses the region.
+__device__ __forceinline__ void rows_to_region(const BlockMem& b, const CUtensorMap* map, int rows, int width, RingCursor& cur,
+                                               int tid, const Giveup& gu) {
+    if (tid == 0) {
+        fence_async();
+        mbar_expect_tx(b.xbar, (uint32_t)rows * (uint32_t)((width + 63) / 64) * 128u);
+        tma_load_3d(b.region, map, 0, 0, 0, b.xbar);
+    }
+    wait_phase(b.xbar, cur.xuse, gu);
+    cur.xuse ^= 1u;
+}
+
+// 1 / rms of every row from the sums of squares that `np` blocks left for it ([np][16] floats), added in a fixed order.
+__device__ __forceinline__ void row_scales(float* inv, const float* ss_part, int np, int M, int H, float eps, int warp, int lane) {
+    for (int m = warp; m < ST_MAX_ROWS; m += ST_WARPS) {
+        float s = 0.f;
+        if (m < M)
+            for (int i = lane; i < np; i += 32) s += __ldcg(ss_part + (size_t)i * ST_MAX_ROWS + m);
+        s = warp_sum(s);
+        if (lane == 0) inv[m] = m < M ? rsqrtf(s / (float)H + eps) : 0.f;
+    }
+}
+
+// What the epilogue of a linear that adds into the residual leaves for the norm after it.
+struct NormFeed {
+    const float* w;   // weight of the next norm (null: nothing follows inside this launch)
+    bf16* xw;         // [M, H]: residual * w, rounded to bfloat16
+    float* ss_part;   // [tiles][16]: this tile's share of every row's sum of squares
+};
+
+// One linear: this block's tiles, the weights from the ring.  XMODE 0: the rows of x lie in the region; 1: chunks of x
+// (512 wide, like the weight stages) come through a ring in the region, asked for by thread 0 a few chunks ahead
+// (`xmap`).  `inv` (optional): every row's result is scaled by inv[row] (the norm's 1 / rms, which commutes with the
+// product).
+template <int NT, int XMODE>
+__device__ __forceinline__ void linear_phase(const StackParams& p, const Linear& lin, const BlockMem& b, RingCursor& cur,
+                                             const CUtensorMap* xmap, bf16* out_bf16, const float* inv, const NormFeed& feed,
+                                             int tid, const Giveup& gu) {
+    constexpr int ROWS = NT * 8;
+    constexpr int RED_STRIDE = ROWS + 1;
+    constexpr int RED_FLOATS = ST_WARPS * 16 * RED_STRIDE;
+    constexpr int XSLOT = ROWS * 1024;       // a chunk of x: eight groups of [ROWS][64]
+    constexpr int XGROUP = ROWS * 128;       // one group
+    const int lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
+    const int ncta = gridDim.x, cta = blockIdx.x;
+    const int K = lin.K, nchunks = (K + ST_KC - 1) / ST_KC;
+    const int n_out = lin.epi == 1 ? lin.N / 2 : lin.N, out_rows = lin.epi == 1 ? 8 : 16;
+    const int stages = p.stages, M = p.M;
+    const int first = (cta + ncta - (int)(cur.deal % (unsigned)ncta)) % ncta;
+    const int mine = first < lin.tiles ? (lin.tiles - first + ncta - 1) / ncta : 0;
+    const unsigned xdepth = (unsigned)b.xdepth, ahead = xdepth - 1;
+    const unsigned xtotal = (unsigned)mine * (unsigned)nchunks;
+    // where the two halves of a tile's 16 rows lie in a stage: one box of 16 rows ([group][16][64]), or, for the stacked
+    // gate/up matrix, two boxes of 8 ([group][8][64] twice)
+    const uint32_t half_stride = lin.epi == 1 ? ST_STAGE_BYTES / 2 : 1024u, group_stride = lin.epi == 1 ? 1024u : 2048u;
+    // this lane's part of the ldmatrix addresses: A takes matrices (rows 0-7 | 8-15) x (k 0-7 | 8-15) of a 16 x 16
+    // block, B the four k eighths of an 8-row, 32-wide block of x
+    const int arow = (lane & 7) + ((lane >> 3) & 1) * 8, akc = lane >> 4, brow = lane & 7, bkc = lane >> 3;
+    const uint32_t a_lane = (uint32_t)(arow >> 3) * half_stride + (uint32_t)(arow & 7) * 128u;
+    int xc = 0;  // chunk index of the next chunk of x to ask for
+    auto x_issue = [&]() {  // thread 0: the next chunk of x into the next slot of the x ring
+        const unsigned slot = cur.xissue;
+        wait_phase(b.xempty + slot, cur.xiparity, gu);
+        mbar_expect_tx(b.xfull + slot, (uint32_t)XSLOT);
+        tma_load_3d(b.region + slot * XSLOT, xmap, 0, 0, xc * (ST_KC / 64), b.xfull + slot);
+        if (++xc == nchunks) xc = 0;
+        if (++cur.xissue == xdepth) { cur.xissue = 0; cur.xiparity ^= 1u; }
+    };
+    if (XMODE == 1 && tid == 0) {
+        fence_async();
+        for (unsigned f = 0; f < ahead && f < xtotal; ++f) x_issue();
+    }
+    unsigned f = 0;
+    for (int tile = first; tile < lin.tiles; tile += ncta) {
+        // a sum of its own for each of the warp's k blocks of a stage: the multiply-adds of a stage do not wait for each other
+        float acc[ST_KB][NT][4];
+#pragma unroll
+        for (int u = 0; u < ST_KB; ++u)
+#pragma unroll
+            for (int t = 0; t < NT; ++t) acc[u][t][0] = acc[u][t][1] = acc[u][t][2] = acc[u][t][3] = 0.f;
+        for (int c = 0; c < nchunks; ++c, ++f) {
+            uint32_t xbase;  // group 0 of this chunk of x
+            unsigned xslot = 0;
+            if (XMODE == 1) {
+                if (tid == 0 && f + ahead < xtotal) x_issue();
+                xslot = cur.xslot;
+                wait_phase(b.xfull + xslot, cur.xparity, gu);
+                xbase = b.region + xslot * XSLOT;
+            } else {
+                xbase = b.region + (uint32_t)c * (ST_KC / 64) * XGROUP;
+            }
+            const unsigned s = cur.slot;
+            wait_phase(b.full + s, cur.parity, gu);
+            const uint32_t st = b.ring + s * ST_STAGE_BYTES;
+            uint32_t a[ST_KB][2][4], bq[ST_KB][NT][4];
+#pragma unroll
+            for (int u = 0; u < ST_KB; ++u) {  // every load of the stage first
+                const int kb = warp * ST_KB + u, ko = kb >> 1, hb = kb & 1;
+#pragma unroll
+                for (int jj = 0; jj < 2; ++jj) {
+                    const int kc = (hb * 2 + jj) * 2 + akc;  // 16-byte chunk of the 128-byte row
+                    ldsm_x4(a[u][jj], st + (uint32_t)ko * group_stride + a_lane + (uint32_t)((kc ^ (arow & 7)) << 4));
+                }
+#pragma unroll
+                for (int t = 0; t < NT; ++t)
+                    ldsm_x4(bq[u][t], xbase + (uint32_t)ko * XGROUP + (uint32_t)(t * 8 + brow) * 128u + (uint32_t)(((hb * 4 + bkc) ^ brow) << 4));
+            }
+#pragma unroll
+            for (int u = 0; u < ST_KB; ++u)
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    mma_bf16(acc[u][t], a[u][0], bq[u][t][0], bq[u][t][1]);
+                    mma_bf16(acc[u][t], a[u][1], bq[u][t][2], bq[u][t][3]);
+                }
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(b.empty + s);
+                if (XMODE == 1) mbar_arrive(b.xempty + xslot);
+            }
+            if (++cur.slot == (unsigned)stages) { cur.slot = 0; cur.parity ^= 1u; }
+            if (XMODE == 1 && ++cur.xslot == xdepth) { cur.xslot = 0; cur.xparity ^= 1u; }
+        }
+#pragma unroll
+        for (int u = 1; u < ST_KB; ++u)  // in k order
+#pragma unroll
+            for (int t = 0; t < NT; ++t)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[0][t][e] += acc[u][t][e];
+        // the tile's sums over the warps, in warp order
+        float* red = b.redbuf + (cur.tiles & 1u) * RED_FLOATS;
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+            float* r0 = red + (warp * 16 + g) * RED_STRIDE + t * 8 + tig * 2;
+            float* r1 = red + (warp * 16 + g + 8) * RED_STRIDE + t * 8 + tig * 2;
+            r0[0] = acc[0][t][0]; r0[1] = acc[0][t][1];
+            r1[0] = acc[0][t][2]; r1[1] = acc[0][t][3];
+        }
+        consumer_sync();
+        for (int idx = tid; idx < out_rows * ROWS; idx += ST_CONSUMERS) {  // whole warps take part or stay out
+            const int m = idx / out_rows, r = idx % out_rows;  // consecutive threads, consecutive columns
+            const int col = tile * out_rows + r;
+            const bool on = m < M && col < n_out;
+            float v = 0.f, u = 0.f;
+#pragma unroll
+            for (int wi = 0; wi < ST_WARPS; ++wi) {
+                v += red[(wi * 16 + r) * RED_STRIDE + m];
+                if (lin.epi == 1) u += red[(wi * 16 + r + 8) * RED_STRIDE + m];
+            }
+            if (lin.epi == 2) {
+                // into the residual; and for the norm after it: the new value times the norm's weight, and the
+                // tile's share of the row's sum of squares (the 16 lanes that hold a row's 16 columns add up)
+                float now = 0.f;
+                if (on) {
+                    float* dst = p.resid + (size_t)m * n_out + col;
+                    now = __ldcg(dst) + v;
+                    __stcg(dst, now);
+                    if (feed.w) feed.xw[(size_t)m * n_out + col] = __float2bfloat16_rn(now * feed.w[col]);
+                }
+                if (feed.w) {
+                    float sq = now * now;
+                    sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+                    sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+                    sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+                    sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+                    if (r == 0) feed.ss_part[(size_t)tile * ST_MAX_ROWS + m] = m < M ? sq : 0.f;
+                }
+            } else if (on) {
+                if (inv) { v *= inv[m]; u *= inv[m]; }
+                if (lin.epi == 1) v = v / (1.f + expf(-v)) * u;
+                out_bf16[(size_t)m * n_out + col] = __float2bfloat16_rn(v);
+            }
+        }
+        ++cur.tiles;  // the other reduction buffer next: this one may still be read
+    }
+    cur.deal += (unsigned)lin.tiles;
+}
+
+// Before the first layer: every row's residual (plus what is still to be added to it) times the first norm's
+// weight, and its sum of squares; a row a block.
+__device__ __forceinline__ void feed_first_norm(const StackParams& p, const float* w, float* scratch, int tid) {
+    const int lane = tid & 31, warp = tid >> 5;
+    for (int m = blockIdx.x; m < p.M; m += gridDim.x) {
+        float* r = p.resid + (size_t)m * p.H;
+        const bf16* d = p.delta ? p.delta + (size_t)m * p.H : nullptr;
+        float ss = 0.f;
+        for (int i = tid * 4; i < p.H; i += ST_CONSUMERS * 4) {
+            float4 v = *reinterpret_cast<const float4*>(r + i);
+            if (d) {
+                float dv[4];
+                load4(d + i, dv);
+                v.x += dv[0]; v.y += dv[1]; v.z += dv[2]; v.w += dv[3];
+                *reinterpret_cast<float4*>(r + i) = v;
+            }
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+            const float4 wv = *reinterpret_cast<const float4*>(w + i);
+            const float ov[4] = {v.x * wv.x, v.y * wv.y, v.z * wv.z, v.w * wv.w};
+            store4(p.xw + (size_t)m * p.H + i, ov);
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) scratch[warp] = ss;
+        consumer_sync();
+        if (tid == 0) {
+            float t = 0.f;
+            for (int wi = 0; wi < ST_WARPS; ++wi) t += scratch[wi];
+            p.ss_part[m] = t;
+        }
+        consumer_sync();
+    }
+}
+
+size_t stack_region_bytes(int M, int xwidth) {
+    const size_t rows_bytes = (size_t)(M <= 8 ? 8 : 16) * (size_t)((xwidth + 63) / 64) * 128;
+    return ((rows_bytes > DEC_MAIN_BYTES ? rows_bytes : DEC_MAIN_BYTES) + 1023) / 1024 * 1024;
+}
+
+__global__ void __launch_bounds__(ST_THREADS, 1)
+decode_stack_kernel(const StackParams p, const __grid_constant__ CUtensorMap map_xw, const __grid_constant__ CUtensorMap map_attn,
+                    const __grid_constant__ CUtensorMap map_act, int region_bytes) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int rows = p.M <= 8 ? 8 : 16;
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    BlockMem b;
+    b.ring = smem_u32(smem);
+    unsigned char* region = smem + (size_t)p.stages * ST_STAGE_BYTES;
+    b.region = smem_u32(region);
+    b.redbuf = reinterpret_cast<float*>(region + region_bytes);
+    const int red_floats = 2 * ST_WARPS * 16 * (rows + 1);
+    b.inv = b.redbuf + ((red_floats + 3) / 4) * 4;
+    b.full = reinterpret_cast<uint64_t*>(b.inv + ST_MAX_ROWS);
+    b.empty = b.full + ST_MAX_STAGES;
+    b.xfull = b.empty + ST_MAX_STAGES;
+    b.xempty = b.xfull + ST_XRING;
+    b.xbar = b.xempty + ST_XRING;
+    int* prefix = reinterpret_cast<int*>(b.xbar + 1);  // [ST_MAX_ROWS + 1]
+    int* s_last = prefix + ST_MAX_ROWS + 1;
+    volatile int* gave_up = s_last + 1;
+    b.xdepth = region_bytes / (rows * 1024);
+    if (b.xdepth > ST_XRING) b.xdepth = ST_XRING;
+    const Giveup gu{gave_up, p.status, 1 + (int)blockIdx.x};
+
+    if (tid == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(b.full + s, 1);
+            mbar_init(b.empty + s, ST_WARPS);
+        }
+        for (int s = 0; s < ST_XRING; ++s) {
+            mbar_init(b.xfull + s, 1);
+            mbar_init(b.xempty + s, ST_WARPS);
+        }
+        mbar_init(b.xbar, 1);
+        *gave_up = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == ST_WARPS) {
+        // ---- the weight stream: this block's tiles of every linear of every layer, in order; one lane does it all
+        if (lane == 0) {
+            uint64_t policy;
+            asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+            unsigned count = 0, deal = 0;
+            unsigned slot = 0, free_parity = 1u;  // the stage that comes next, the parity of its "free" phase
+            unsigned gate = 0, gate_parity = 0u;  // the stage `inflight` before it, the parity of its "landed" phase
+            const int ncta = gridDim.x, cta = blockIdx.x;
+            bool on = true;
+            for (int l = 0; l < p.num_layers && on; ++l) {
+                for (int phase = 0; phase < 4 && on; ++phase) {
+                    const Linear lin = phase_linear(p, p.layers + l, phase);
+                    const int n_out = lin.epi == 1 ? lin.N / 2 : lin.N;
+                    const int nchunks = (lin.K + ST_KC - 1) / ST_KC;
+                    const int first = (cta + ncta - (int)(deal % (unsigned)ncta)) % ncta;
+                    for (int tile = first; tile < lin.tiles && on; tile += ncta) {
+                        for (int c = 0; c < nchunks; ++c) {
+                            if (!wait_phase(b.empty + slot, free_parity, gu)) { on = false; break; }
+                            if (count >= (unsigned)p.inflight) {  // not too much on its way at once
+                                if (!wait_phase(b.full + gate, gate_parity, gu)) { on = false; break; }
+                                if (++gate == (unsigned)p.stages) { gate = 0; gate_parity ^= 1u; }
+                            }
+                            const uint32_t dst = b.ring + slot * ST_STAGE_BYTES;
+                            mbar_expect_tx(b.full + slot, (uint32_t)ST_STAGE_BYTES);  // rows and k beyond the matrix arrive as zeros
+                            if (lin.epi == 1) {
+                                tma_load_3d_hint(dst, lin.map, 0, tile * 8, c * (ST_KC / 64), b.full + slot, policy);
+                                tma_load_3d_hint(dst + ST_STAGE_BYTES / 2, lin.map, 0, n_out + tile * 8, c * (ST_KC / 64), b.full + slot, policy);
+                            } else {
+                                tma_load_3d_hint(dst, lin.map, 0, tile * 16, c * (ST_KC / 64), b.full + slot, policy);
+                            }
+                            ++count;
+                            if (++slot == (unsigned)p.stages) { slot = 0; free_parity ^= 1u; }
+                        }
+                    }
+                    deal += (unsigned)lin.tiles;
+                }
+            }
+            // nothing this lane asked for may still be on its way when the block leaves
+            const unsigned issued = count, back = issued < (unsigned)p.stages ? issued : (unsigned)p.stages;
+            for (unsigned i = issued - back; i < issued; ++i)
+                wait_phase(b.full + i % (unsigned)p.stages, (i / (unsigned)p.stages) & 1u, gu, false);
+        }
+    } else {
+        // ---- the arithmetic
+        const int NT = p.M <= 8 ? 1 : 2;
+        const CacheLayout L{p.nkv, p.page_size, D};
+        bf16* qtile = reinterpret_cast<bf16*>(region);
+        bf16* tiles = qtile + 16 * LDS;
+        unsigned long long target = 0;
+        if (tid == 0) {
+            const unsigned long long per_launch = ((unsigned long long)p.num_layers * 5ull + 1ull) * gridDim.x;
+            target = ld_acquire(p.arrivals) / per_launch * per_launch;  // what it was when the launch began
+        }
+        if (warp < DEC_WARPS) flat_prefix<BAR_ATTENTION>(prefix, p.meta, p.cu_tokens, p.positions, p.S, p.window, tid);
+        RingCursor cur{0u, 0u, 0u, 0u, 0u, 0u, 0u, 1u, 0u};
+        const int q_stride = (p.nq + 2 * p.nkv) * D;
+        const int hidden_tiles = (p.H + 15) / 16;
+        const NormFeed none{nullptr, nullptr, nullptr};
+        feed_first_norm(p, p.layers[0].norm1, b.redbuf, tid);
+        grid_barrier(p, target, tid, gu);
+        int np = 1;  // blocks that left a share of the rows' sums of squares
+        for (int l = 0; l < p.num_layers; ++l) {
+            const StackLayer* ly = p.layers + l;
+            // 1. the normed rows (their scale applied to the products), q/k/v
+            rows_to_region(b, &map_xw, rows, p.H, cur, tid, gu);
+            row_scales(b.inv, p.ss_part, np, p.M, p.H, p.eps, warp, lane);
+            consumer_sync();
+            if (NT == 1) linear_phase<1, 0>(p, phase_linear(p, ly, 0), b, cur, nullptr, p.qkv, b.inv, none, tid, gu);
+            else linear_phase<2, 0>(p, phase_linear(p, ly, 0), b, cur, nullptr, p.qkv, b.inv, none, tid, gu);
+            stamp(p, l, 0, tid);
+            grid_barrier(p, target, tid, gu);
+            stamp(p, l, 1, tid);
+            // 2. attention
+            if (warp < DEC_WARPS)
+                flat_attention<BAR_ATTENTION>(blockIdx.x, gridDim.x, tid, qtile, tiles, prefix, s_last, p.qkv, q_stride, ly->cache, L, p.meta,
+                                              p.group, p.cu_tokens, p.positions, p.attn_out, p.part_o, p.part_ml, p.counters, ly->inv_freq,
+                                              p.rot, ly->store_kv, p.nq, p.window, p.scale_log2, p.num_pages, p.S, p.status);
+            stamp(p, l, 2, tid);
+            grid_barrier(p, target, tid, gu);
+            stamp(p, l, 3, tid);
+            // 3. output projection into the residual; feeds the second norm
+            {
+                const NormFeed feed{ly->norm2, p.xw, p.ss_part};
+                rows_to_region(b, &map_attn, rows, p.nq * D, cur, tid, gu);
+                if (NT == 1) linear_phase<1, 0>(p, phase_linear(p, ly, 1), b, cur, nullptr, nullptr, nullptr, feed, tid, gu);
+                else linear_phase<2, 0>(p, phase_linear(p, ly, 1), b, cur, nullptr, nullptr, nullptr, feed, tid, gu);
+                np = hidden_tiles;
+            }
+            stamp(p, l, 4, tid);
+            grid_barrier(p, target, tid, gu);
+            stamp(p, l, 5, tid);
+            // 4. the normed rows, gate/up with SwiGLU
+            rows_to_region(b, &map_xw, rows, p.H, cur, tid, gu);
+            row_scales(b.inv, p.ss_part, np, p.M, p.H, p.eps, warp, lane);
+            consumer_sync();
+            if (NT == 1) linear_phase<1, 0>(p, phase_linear(p, ly, 2), b, cur, nullptr, p.act, b.inv, none, tid, gu);
+            else linear_phase<2, 0>(p, phase_linear(p, ly, 2), b, cur, nullptr, p.act, b.inv, none, tid, gu);
+            stamp(p, l, 6, tid);
+            grid_barrier(p, target, tid, gu);
+            stamp(p, l, 7, tid);
+            // 5. down projection into the residual; feeds the next layer's first norm
+            {
+                const NormFeed feed{l + 1 < p.num_layers ? p.layers[l + 1].norm1 : nullptr, p.xw, p.ss_part};
+                if (NT == 1) linear_phase<1, 1>(p, phase_linear(p, ly, 3), b, cur, &map_act, nullptr, nullptr, feed, tid, gu);
+                else linear_phase<2, 1>(p, phase_linear(p, ly, 3), b, cur, &map_act, nullptr, nullptr, feed, tid, gu);
+            }
+            stamp(p, l, 8, tid);
+            grid_barrier(p, target, tid, gu);
+            stamp(p, l, 9, tid);
+        }
+    }
+    asm volatile("bar.sync %0, %1;" ::"n"(BAR_ALL), "n"(ST_THREADS) : "memory");
+}
+
+// ----------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* q = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &q, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(q);
+    }
+    return fn;
+}
+
+// A [rows, K] bfloat16 row-major matrix (K a multiple of 64) seen as [K / 64][rows][64], boxes of `groups` x
+// `box_rows` x 64 with the 128-byte swizzle; what lies beyond the matrix arrives as zeros.
+bool make_map(CUtensorMap* map, const void* base, long long rows, long long K, int box_rows, int groups) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn || K % 64 || rows <= 0 || ((uintptr_t)base & 15)) return false;
+    alignas(64) CUtensorMap tmp;
+    cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(K / 64)};
+    cuuint64_t strides[2] = {(cuuint64_t)K * 2, 128};
+    cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)groups};
+    cuuint32_t estr[3] = {1, 1, 1};
+    if (fn(&tmp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    memcpy(map, &tmp, sizeof(tmp));
+    return true;
+}
+
+size_t stack_fixed_smem(int M, int xwidth) {
+    const size_t red = (size_t)((2 * ST_WARPS * 16 * ((M <= 8 ? 8 : 16) + 1) + 3) / 4) * 4 * sizeof(float);
+    return stack_region_bytes(M, xwidth) + red + ST_MAX_ROWS * sizeof(float) + (2 * ST_MAX_STAGES + 2 * ST_XRING + 1) * sizeof(uint64_t) +
+           (ST_MAX_ROWS + 1 + 2) * sizeof(int) + 1024 + 64;
+}
+
+struct StackPlan { int blocks, stages; size_t smem; };
+// Grid and ring depth for M rows of width xwidth (the larger of the model's width and heads x head size) on the
+// current device; blocks == 0: this geometry does not fit.
+StackPlan stack_plan(int M, int xwidth) {
+    StackPlan plan{0, 0, 0};
+    int dev = 0, sms = 0, per_sm = 0, smem_max = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return plan;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return plan;
+    if (cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) return plan;
+    const size_t fixed = stack_fixed_smem(M, xwidth);
+    if (fixed + (size_t)ST_MIN_STAGES * ST_STAGE_BYTES > (size_t)smem_max) return plan;
+    int stages = (int)(((size_t)smem_max - fixed) / ST_STAGE_BYTES);
+    if (stages > ST_MAX_STAGES) stages = ST_MAX_STAGES;
+    const size_t smem = fixed + (size_t)stages * ST_STAGE_BYTES;
+    static size_t configured[64] = {};
+    if (dev < 0 || dev >= 64) return plan;
+    if (smem > configured[dev]) {
+        if (cudaFuncSetAttribute(decode_stack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return plan;
+        configured[dev] = smem;
+    }
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, decode_stack_kernel, ST_THREADS, smem) != cudaSuccess || per_sm < 1) return plan;
+    plan.blocks = sms;
+    plan.stages = stages;
+    plan.smem = smem;
+    return plan;
+}
+
+}  // namespace
+
+extern "C" int decode_stack_head_dim() { return D; }
+extern "C" int decode_stack_layer_bytes() { return (int)sizeof(StackLayer); }
+extern "C" int decode_stack_max_rows() { return ST_MAX_ROWS; }
+
+// Writes one layer's descriptor (decode_stack_layer_bytes() bytes, host memory; the table of all layers then goes to
+// the device, which must keep it on a 64-byte boundary).  Weights are bfloat16, row-major: w_qkv [(nq + 2 nkv) D, H],
+// w_o [H, nq D], w_gate_up [2 I, H] (gate rows, then up rows), w_down [H, I]; H, nq D and I multiples of 64.
+// 0, or an error (the widths, or a tensor map the driver refused).
+extern "C" int decode_stack_fill_layer(void* dst, const void* w_qkv, const void* w_o, const void* w_gate_up, const void* w_down,
+                                       const float* norm1, const float* norm2, const float* inv_freq, void* cache, int store_kv,
+                                       int H, int I, int nq, int nkv) {
+    StackLayer ly;
+    memset(&ly, 0, sizeof(ly));
+    if (H % 64 || I % 64 || (nq * D) % 64) return (int)cudaErrorInvalidValue;
+    if (!make_map(&ly.map_qkv, w_qkv, (long long)(nq + 2 * nkv) * D, H, 16, ST_KC / 64) || !make_map(&ly.map_o, w_o, H, (long long)nq * D, 16, ST_KC / 64) ||
+        !make_map(&ly.map_gate_up, w_gate_up, 2ll * I, H, 8, ST_KC / 64) || !make_map(&ly.map_down, w_down, H, I, 16, ST_KC / 64))
+        return (int)cudaErrorInvalidValue;
+    ly.norm1 = norm1; ly.norm2 = norm2; ly.inv_freq = inv_freq; ly.cache = (bf16*)cache; ly.store_kv = store_kv;
+    memcpy(dst, &ly, sizeof(ly));
+    return 0;
+}
+
+// For measurements: how many stages a block may have on their way at once (0: the default).
+extern "C" void decode_stack_set_inflight(int stages) { g_stack_inflight = stages; }
+
+// For measurements: a device buffer of blocks * layers * 10 64-bit words in which every block leaves the global
+// clock after each phase and each barrier of each layer (null: off, the default).  Reading that clock costs a few
+// hundred nanoseconds each time.
+extern "C" void decode_stack_set_times(long long* buffer) { g_stack_times = buffer; }
+
+// Blocks of the kernel for M rows of width xwidth = max(H, nq * head size) (0: the geometry does not fit this device's
+// shared memory).
+extern "C" int decode_stack_blocks(int M, int xwidth) { return stack_plan(M, xwidth).blocks; }
+
+// Floats of scratch for the attention's partial results.
+extern "C" size_t decode_stack_scratch_floats(int S, int nq, int nkv, int blocks) {
+    return (size_t)(blocks + S * nkv) * (nq / nkv) * (D + 2);
+}
+
+// Runs `num_layers` layers (descriptors `layers` in device memory, written by decode_stack_fill_layer) on the M = S
+// rows of a decode step.  resid [M, H] float32 is updated in place; delta (optional, bfloat16 [M, H]) is added to it
+// on the way.  qkv, attn_out, act, xw ([M, H]): bfloat16 workspaces of M rows, 16-byte aligned; ss_part:
+// ceil(H / 16) * 16 floats; scratch: decode_stack_scratch_floats(...) floats; counters: S * nkv ints, zero (left zero);
+// arrivals: one 64-bit counter that belongs to this (layers, device) pair alone and starts at zero.
+extern "C" int decode_stack(const void* layers, int num_layers, void* resid, const void* delta, void* qkv, void* attn_out,
+                            void* act, void* xw, float* ss_part, float* scratch, int* counters, unsigned long long* arrivals,
+                            const int* meta, int group, const int* cu_tokens, const int* positions, int M, int S, int H, int I,
+                            int nq, int nkv, int rot, int window, int page_size, int num_pages, float eps, float scale,
+                            int* status, cudaStream_t stream) {
+    if (num_layers <= 0 || M <= 0) return 0;
+    if (M > ST_MAX_ROWS || S != M || H % 64 || I % 64 || (nq * D) % 64 || nq % nkv || nq / nkv > 16 || rot % 2 || rot > D || rot <= 0 ||
+        ((uintptr_t)layers & 63))
+        return (int)cudaErrorInvalidValue;
+    const int xwidth = H > nq * D ? H : nq * D;
+    const StackPlan plan = stack_plan(M, xwidth);
+    if (!plan.blocks) return (int)cudaErrorInvalidConfiguration;
+    const int rows = M <= 8 ? 8 : 16;
+    CUtensorMap map_xw, map_attn, map_act;
+    if (H / 64 > 256 || nq * D / 64 > 256) return (int)cudaErrorInvalidValue;  // a box has at most 256 groups
+    if (!make_map(&map_xw, xw, M, H, rows, H / 64) || !make_map(&map_attn, attn_out, M, (long long)nq * D, rows, nq * D / 64) ||
+        !make_map(&map_act, act, M, I, rows, ST_KC / 64))
+        return (int)cudaErrorInvalidValue;
+    StackParams p;
+    p.layers = (const StackLayer*)layers;
+    p.resid = (float*)resid;
+    p.delta = (const bf16*)delta;
+    p.qkv = (bf16*)qkv;
+    p.attn_out = (bf16*)attn_out;
+    p.act = (bf16*)act;
+    p.xw = (bf16*)xw;
+    p.ss_part = ss_part;
+    const size_t slots = (size_t)plan.blocks + (size_t)S * nkv;
+    p.part_o = scratch;
+    p.part_ml = scratch + slots * (nq / nkv) * D;
+    p.counters = counters;
+    p.arrivals = arrivals;
+    p.meta = meta;
+    p.cu_tokens = cu_tokens;
+    p.positions = positions;
+    p.status = status;
+    p.num_layers = num_layers; p.group = group; p.M = M; p.H = H; p.I = I; p.nq = nq; p.nkv = nkv; p.rot = rot;
+    p.window = window; p.num_pages = num_pages; p.page_size = page_size; p.S = S; p.stages = plan.stages;
+    p.eps = eps; p.scale_log2 = scale * LOG2E;
+    p.times = g_stack_times;
+    p.inflight = g_stack_inflight > 0 ? g_stack_inflight : ST_INFLIGHT;
+    if (p.inflight > p.stages) p.inflight = p.stages;
+    const int region_bytes = (int)stack_region_bytes(M, xwidth);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(plan.blocks, 1, 1);
+    cfg.blockDim = dim3(ST_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = plan.smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;  // all blocks resident at once: they wait for each other
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t err = cudaLaunchKernelEx(&cfg, decode_stack_kernel, p, map_xw, map_attn, map_act, region_bytes);
+    if (err != cudaSuccess) return (int)err;
+    LAUNCH_RETURN();
+}

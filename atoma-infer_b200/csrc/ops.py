@@ -21,13 +21,14 @@ DT_F32, DT_BF16 = 0, 1
 META_HEADER_INTS = 20
 META_NUM_TOKENS, META_NUM_ENTRIES, META_NUM_ROWS, META_BT_STRIDE, META_BT_OFFSET = 0, 1, 2, 4, 12
 MAX_GROUPS = 8
-STATUS_WORDS = 4
+STATUS_WORDS = 8
 SKINNY_MAX_ROWS = 16  # bfloat16 linears with at most this many rows stream the weights
 
 CORE_SOURCES = ["kernels/core.cu", "kernels/linear_bf16.cu", "kernels/sampling.cu"]
 ATTENTION_SOURCES = ["kernels/attention_bf16.cu"]
 GEMM_SOURCES = ["kernels/gemm_tcgen05.cu"]
 ATTENTION_TC_SOURCES = ["kernels/attention_tcgen05.cu"]
+DECODE_STACK_SOURCES = ["kernels/decode_stack.cu"]
 ATTENTION_TC_HEAD_DIMS = (64, 128)  # head sizes of the tcgen05 prefill attention
 ATTENTION_HEAD_DIMS = tuple(range(16, 257, 16))  # every head size the kernels take; the build check builds them all, a model only its own
 
@@ -85,6 +86,10 @@ class CudaOps:
         mode = os.environ.get("ATOMA_INFER_PDL", "linear+norm")
         self.pdl = {"0": 0, "1": 1, "linear": 2, "linear+norm": 6}.get(mode, 6)
         self.fused_rope = True  # the decode attention rotates q and k and writes the new key and value itself
+        # Decode steps of at most 16 rows can run stretches of whole layers as one persistent kernel (ATOMA_INFER_FUSED_LAYERS=1;
+        # off by default while it is slower than the step part by part)
+        self.fused_layers = os.environ.get("ATOMA_INFER_FUSED_LAYERS", "0") == "1"
+        self._stack_libs, self._stack_blocks = {}, {}
         # Before the decode attention of a small batch the weight of the linear after it is asked into L2 if it has
         # at most this many bytes (0: never); see _prefetch_next_weight.
         self.prefetch_bytes = int(float(os.environ.get("ATOMA_INFER_PREFETCH_MB", "12")) * (1 << 20))
@@ -116,7 +121,9 @@ class CudaOps:
         return (f"token id out of range at token {s[0] - 1}" if s[0] else
                 f"block table names no valid page for token {s[1] - 1}" if s[1] else
                 f"a tensor-core GEMM block ({s[2] - 1}) gave up waiting on a barrier" if s[2] else
-                f"a tensor-core attention block ({s[3] - 1}) gave up waiting on a barrier")
+                f"a tensor-core attention block ({s[3] - 1}) gave up waiting on a barrier" if s[3] else
+                f"a block ({s[4] - 1}) of the decode step's layer kernel gave up waiting" if s[4] else
+                f"status words {s}")
 
     def clear_status(self) -> None:
         self.status.zero_()
@@ -319,6 +326,67 @@ class CudaOps:
                                           _p(ctx.token_entry), _p(ctx.positions), _p(out), T, nq, nkv, d, page_size,
                                           num_pages, window, ctypes.c_float(scale), _p(self.status), self._stream()),
                     "attn_generic")
+
+    # ------------------------------------------------------------------ whole layers of a decode step
+    def _decode_stack_library(self, d: int):
+        lib = self._stack_libs.get(d)
+        if lib is None:
+            lib = build.load_library(f"decode_stack_d{d}", DECODE_STACK_SOURCES, cuda=True, defines={"HEAD_DIM": d})
+            lib.decode_stack_scratch_floats.restype = ctypes.c_size_t
+            if lib.decode_stack_head_dim() != d:
+                raise KernelError(f"decode stack library was built for head size {lib.decode_stack_head_dim()}, wanted {d}")
+            self._stack_libs[d] = lib
+        return lib
+
+    def decode_stack_layers(self, layers, *, d: int, hidden: int, intermediate: int, nq: int, nkv: int) -> torch.Tensor:
+        """The layer kernel's descriptors on the device, one per dict of ``layers`` (tensors ``w_qkv``, ``w_o``,
+        ``w_gate_up``, ``w_down``, ``norm1``, ``norm2``, ``inv_freq``, ``cache``; bool ``store_kv``)."""
+        lib = self._decode_stack_library(d)
+        size = int(lib.decode_stack_layer_bytes())
+        host = torch.zeros(len(layers) * size, dtype=torch.uint8)
+        for i, ly in enumerate(layers):
+            err = lib.decode_stack_fill_layer(ctypes.c_void_p(host.data_ptr() + i * size), _p(ly["w_qkv"]), _p(ly["w_o"]),
+                                              _p(ly["w_gate_up"]), _p(ly["w_down"]), _p(ly["norm1"]), _p(ly["norm2"]),
+                                              _p(ly["inv_freq"]), _p(ly["cache"]), int(ly["store_kv"]), hidden, intermediate,
+                                              nq, nkv)
+            if err:
+                raise KernelError(f"decode_stack_fill_layer: error {err} (widths must be multiples of 64)")
+        return host.to(self.device)
+
+    def decode_stack_blocks(self, d: int, rows: int, hidden: int) -> int:
+        """Blocks the layer kernel would run with for ``rows`` rows of width ``hidden`` (the larger of the model's
+        width and heads x head size; 0: it does not take them)."""
+        key = (d, rows <= 8, hidden)
+        n = self._stack_blocks.get(key)
+        if n is None:
+            ok = d % 16 == 0 and 16 <= d <= 256 and hidden % 8 == 0
+            n = self._stack_blocks[key] = int(self._decode_stack_library(d).decode_stack_blocks(rows, hidden)) if ok else 0
+        return n if rows <= SKINNY_MAX_ROWS else 0
+
+    def decode_stack(self, layers, num_layers: int, resid, delta, arrivals, ctx, group: int, *, hidden: int, intermediate: int,
+                     nq: int, nkv: int, d: int, rot: int, window: int, page_size: int, num_pages: int, eps: float,
+                     scale: float):
+        """``num_layers`` pre-norm layers (RMSNorm, rotary attention over the paged cache, SwiGLU) of a decode step in
+        one launch (kernels/decode_stack.cu): resid [rows, hidden] float32 is updated in place, ``delta`` added first."""
+        lib = self._decode_stack_library(d)
+        M = ctx.T
+        blocks = self.decode_stack_blocks(d, M, max(hidden, nq * d))
+        if not blocks or ctx.S != M or not ctx.decode_only:
+            raise KernelError("the decode layer kernel takes decode steps of at most 16 rows")
+        if M * nkv > self._counters.numel():
+            raise KernelError(f"decode layers: {M} requests x {nkv} heads exceed the split counters")
+        dev = resid.device
+        qkv = torch.empty((M, (nq + 2 * nkv) * d), dtype=torch.bfloat16, device=dev)
+        out = torch.empty((M, nq * d), dtype=torch.bfloat16, device=dev)
+        act = torch.empty((M, intermediate), dtype=torch.bfloat16, device=dev)
+        xw = torch.empty((M, hidden), dtype=torch.bfloat16, device=dev)
+        ss_part = torch.empty(-(-hidden // 16) * 16, dtype=torch.float32, device=dev)
+        scratch = torch.empty(lib.decode_stack_scratch_floats(M, nq, nkv, blocks), dtype=torch.float32, device=dev)
+        self._check(lib.decode_stack(_p(layers), num_layers, _p(resid), _p(delta), _p(qkv), _p(out), _p(act), _p(xw), _p(ss_part), _p(scratch),
+                                     _p(self._counters), _p(arrivals), _p(ctx.meta), group, _p(ctx.cu_tokens), _p(ctx.positions),
+                                     M, ctx.S, hidden, intermediate, nq, nkv, rot, window, page_size, num_pages,
+                                     ctypes.c_float(eps), ctypes.c_float(scale), _p(self.status), self._stream()),
+                    "decode_stack")
 
     def _decode_flat_blocks(self, lib, d: int, S: int, nkv: int) -> int:
         """Grid size of the flat decode kernel if this batch should take it (at least half as many (request,

@@ -77,6 +77,14 @@ class Attention(Mixer):
         self.w_o = tensors[pre + ".o_proj.weight"].contiguous()
         self.position.bind(tensors, rt)
 
+    def fused(self):
+        rotary = self.position.rotary()
+        if rotary is None:
+            return None
+        return {"kind": "attention", "w_qkv": self.w_qkv, "w_o": self.w_o, "hidden": self.hidden,
+                "num_heads": self.num_heads, "num_kv_heads": self.num_kv_heads, "head_dim": self.head_dim,
+                "scale": self.scale, "window": int(self.window or 0), "inv_freq": rotary[0], "rotary_dim": rotary[1]}
+
     def forward(self, x, ctx, cache):
         ops = self.rt.ops
         qkv = ops.linear(x, self.w_qkv, meta=ctx.meta)

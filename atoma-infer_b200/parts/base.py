@@ -101,6 +101,11 @@ class Part:
         model's width); the engine sizes its working memory from it when it sizes the cache."""
         return 0
 
+    def fused(self) -> Optional[Dict[str, Any]]:
+        """What a kernel that runs several parts at once needs to know of this part (after ``bind``): a dict with
+        ``kind``, the part's tensors and constants.  None (the default): the part only runs through ``forward``."""
+        return None
+
 
 class Embedding(Part):
     """The first stage: the step's token ids (and whatever else of the step's metadata it wants, positions
@@ -189,3 +194,8 @@ class Block(Part):
     def forward(self, resid: torch.Tensor, delta: Optional[torch.Tensor], ctx: StepContext,
                 cache: LayerCache) -> torch.Tensor:
         raise NotImplementedError
+
+    def decode_fusion(self) -> Optional[Dict[str, Any]]:
+        """For a kernel that runs a run of whole layers of a decode step: this block's arrangement and what its
+        parts say of themselves (``Part.fused``), or None if the block, or one of its parts, cannot take part."""
+        return None

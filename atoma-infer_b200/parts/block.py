@@ -41,6 +41,13 @@ class PreNormBlock(Block):
         for p in self.parts():
             p.bind(tensors, rt)
 
+    def decode_fusion(self):
+        parts = {"norm1": self.norm1.fused(), "mixer": self.mixer.fused(), "norm2": self.norm2.fused(),
+                 "feed_forward": self.feed_forward.fused()}
+        if any(v is None for v in parts.values()):
+            return None
+        return {"kind": "prenorm", **parts}
+
     def forward(self, resid, delta, ctx, cache):
         h = self.norm1.forward(resid, delta, ctx)
         a = self.mixer.forward(h, ctx, cache)

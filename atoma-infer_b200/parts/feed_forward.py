@@ -39,6 +39,10 @@ class SwiGLU(FeedForward):
     def streamed_weights(self):
         return [self.w_gate_up, self.w_down]
 
+    def fused(self):
+        return {"kind": "swiglu", "w_gate_up": self.w_gate_up, "w_down": self.w_down, "hidden": self.hidden,
+                "intermediate": self.intermediate}
+
     def forward(self, x, ctx):
         ops = self.rt.ops
         act = ops.linear(x, self.w_gate_up, silu_mul=True, meta=ctx.meta)

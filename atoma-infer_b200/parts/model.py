@@ -19,6 +19,7 @@ from ..cache.spec import CacheGroup, CacheNeed
 from ..config.registry import part_class
 from ..weights.loader import TensorDecl
 from .base import LayerCache, Runtime, StepContext
+from .decode_stack import MAX_ROWS as STACK_MAX_ROWS, plan_stacks
 
 # the registrations of the built-in parts
 from . import attention, block, embedding, feed_forward, head, norm, position  # noqa: F401
@@ -150,6 +151,8 @@ class DecoderModel:
         if hasattr(rt.ops, "set_weight_order"):  # the step's weight stream, in order of use
             order = [w for r in self.runs for w in self.blocks[r.layer].streamed_weights()]
             rt.ops.set_weight_order(order + self.head.streamed_weights())
+        # stretches of the schedule that a decode step of few rows runs as one launch
+        self.stacks = plan_stacks(self.blocks, self.runs, self.run_owner, self.run_group, rt)
 
     # ------------------------------------------------------------------ the forward pass of one step
     def forward(self, ctx: StepContext, cache, rows: torch.Tensor, num_rows: int) -> torch.Tensor:
@@ -157,9 +160,18 @@ class DecoderModel:
         at the flat-batch rows listed in ``rows`` (a device int32 array)."""
         resid = self.embedding.forward(ctx)
         delta = None
-        for i, run in enumerate(self.runs):
-            view = cache.layer_view(self.run_owner[i], writes=run.cache_of is None, state_run=i)
-            delta = self.blocks[run.layer].forward(resid, delta, ctx, view)
+        view_of = lambda k: cache.layer_view(self.run_owner[k], writes=self.runs[k].cache_of is None, state_run=k)  # noqa: E731
+        stacks = self.stacks if (self.stacks and ctx.decode_only and ctx.T == ctx.S and ctx.T <= STACK_MAX_ROWS
+                                 and getattr(self.rt.ops, "fused_layers", False)) else {}
+        i = 0
+        while i < len(self.runs):
+            stack = stacks.get(i)
+            if stack is not None and stack.supports(ctx.T):
+                stack.forward(resid, delta, ctx, [view_of(k) for k in range(stack.first, stack.end)])
+                delta, i = None, stack.end
+                continue
+            delta = self.blocks[self.runs[i].layer].forward(resid, delta, ctx, view_of(i))
+            i += 1
         if num_rows == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
         h = self.final_norm.forward(resid, delta, ctx, rows=rows, num_rows=num_rows)

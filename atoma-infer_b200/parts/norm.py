@@ -32,5 +32,8 @@ class RMSNorm(Norm):
         self.rt.ops.add_rmsnorm(resid, delta, self.weight, self.eps, out, ctx.meta, n, rows=rows)
         return out
 
+    def fused(self):
+        return {"kind": "rmsnorm", "weight": self.weight, "eps": self.eps, "size": self.size}
+
 
 register_part("norm", "rmsnorm", RMSNorm)
