@@ -136,9 +136,10 @@ def host_library() -> ctypes.CDLL:
 def all_kernel_libraries():
     """(name, sources, defines) of every kernel library, for the build check."""
     from .ops import (ATTENTION_HEAD_DIMS, ATTENTION_SOURCES, ATTENTION_TC_HEAD_DIMS, ATTENTION_TC_SOURCES, CORE_SOURCES,
-                      GEMM_SOURCES)
+                      DECODE_STACK_SOURCES, GEMM_SOURCES)
 
     return [("core", CORE_SOURCES, None), ("gemm_tcgen05", GEMM_SOURCES, None)] + [
         (f"attention_d{d}", ATTENTION_SOURCES, {"HEAD_DIM": d}) for d in ATTENTION_HEAD_DIMS] + [
         (f"attention_noalloc_d{d}", ["kernels/attention_noalloc.cu"], {"HEAD_DIM": d}) for d in (64, 128)] + [
-        (f"attention_tc_d{d}", ATTENTION_TC_SOURCES, {"HEAD_DIM": d}) for d in ATTENTION_TC_HEAD_DIMS]
+        (f"attention_tc_d{d}", ATTENTION_TC_SOURCES, {"HEAD_DIM": d}) for d in ATTENTION_TC_HEAD_DIMS] + [
+        (f"decode_stack_d{d}", DECODE_STACK_SOURCES, {"HEAD_DIM": d}) for d in (64, 128)]

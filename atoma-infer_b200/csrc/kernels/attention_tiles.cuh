@@ -238,6 +238,101 @@ constexpr size_t DEC_SMEM = DEC_MAIN_BYTES;
 constexpr int DEC_BLOCKS_PER_SM = (int)((227 * 1024) / (DEC_SMEM + 1024)) < 8 ? (int)((227 * 1024) / (DEC_SMEM + 1024)) : 8;
 }  // namespace
 
+namespace {
+// The end of a segment of a decode attention: the NW warps' partial results (m, l, o of the rows g and g + 8 of each
+// thread's quad) merged in warp order; the segment's result written out if it covers its (request, head group) pair
+// alone (parts == 1), else left in scratch slot (block + pair) and counted in, the last segment to arrive for the pair
+// merging the pair's slots (first_block + pair ...) in order.  mbuf: NW * (32 + 16 * D) floats of shared memory that
+// every warp is done using; the NW * 32 threads meet at hardware barrier BAR.
+template <int BAR, int NW> __device__ __forceinline__ void seg_sync() { asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(NW * 32) : "memory"); }
+template <int BAR, int NW>
+__device__ __forceinline__ void decode_segment_finish(float* mbuf, int tid, const float (&m)[2], const float (&l)[2],
+                                                      const float (&o)[DTILES][4], int parts, int pair, int first_block, int block,
+                                                      int row0, int kvh, int G, int nq, bf16* __restrict__ out,
+                                                      float* __restrict__ part_o, float* __restrict__ part_ml,
+                                                      int* __restrict__ counters, int* s_last) {
+    const int lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
+    float* wm = mbuf + warp * (32 + 16 * D);  // m[16], l[16], o[16][D]
+    if (tig == 0) {
+        wm[g] = m[0]; wm[g + 8] = m[1];
+        wm[16 + g] = l[0]; wm[16 + g + 8] = l[1];
+    }
+#pragma unroll
+    for (int dt = 0; dt < DTILES; ++dt) {
+        int dim = dt * 8 + tig * 2;
+        wm[32 + g * D + dim] = o[dt][0]; wm[32 + g * D + dim + 1] = o[dt][1];
+        wm[32 + (g + 8) * D + dim] = o[dt][2]; wm[32 + (g + 8) * D + dim + 1] = o[dt][3];
+    }
+    seg_sync<BAR, NW>();
+    const size_t slot = (size_t)block + pair;
+    for (int idx = tid; idx < G * D; idx += NW * 32) {
+        int r = idx / D, i = idx % D;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) mx = fmaxf(mx, mbuf[w * (32 + 16 * D) + r]);
+        float lsum = 0.f, acc = 0.f;
+        if (mx > -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < NW; ++w) {
+                const float* p = mbuf + w * (32 + 16 * D);
+                float f = fast_exp2(p[r] - mx);
+                lsum += p[16 + r] * f;
+                acc += p[32 + r * D + i] * f;
+            }
+        }
+        if (parts == 1) {
+            out[((size_t)row0 * nq + kvh * G + r) * D + i] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+        } else {
+            part_o[(slot * G + r) * D + i] = acc;
+            if (i == 0) { part_ml[(slot * G + r) * 2] = mx; part_ml[(slot * G + r) * 2 + 1] = lsum; }
+        }
+    }
+    if (parts > 1) {
+        // count this segment in; the last one merges the pair's slots (first_block + pair ... in order)
+        __threadfence();
+        seg_sync<BAR, NW>();
+        if (tid == 0) {
+            int old = atomicAdd(counters + pair, 1);
+            (*s_last) = old == parts - 1;
+            if ((*s_last)) counters[pair] = 0;  // as it was found, for the next launch
+        }
+        seg_sync<BAR, NW>();
+        if ((*s_last)) {
+            __threadfence();
+            const size_t slot0 = (size_t)first_block + pair;
+            for (int idx = tid; idx < G * D; idx += NW * 32) {
+                int r = idx / D, i = idx % D;
+                float mx = -INFINITY;
+                for (int sp = 0; sp < parts; ++sp) mx = fmaxf(mx, __ldcg(part_ml + ((slot0 + sp) * G + r) * 2));
+                float lsum = 0.f, acc = 0.f;
+                if (mx > -INFINITY) {
+                    for (int s0 = 0; s0 < parts; s0 += 4) {
+                        float pm[4], pl[4], po[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {  // independent loads, in flight together
+                            const bool on = s0 + j < parts;
+                            const size_t sl = slot0 + (on ? s0 + j : 0);
+                            pm[j] = on ? __ldcg(part_ml + (sl * G + r) * 2) : -INFINITY;
+                            pl[j] = on ? __ldcg(part_ml + (sl * G + r) * 2 + 1) : 0.f;
+                            po[j] = on ? __ldcg(part_o + (sl * G + r) * D + i) : 0.f;
+                        }
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            if (s0 + j < parts) {
+                                float f = fast_exp2(pm[j] - mx);
+                                lsum += pl[j] * f;
+                                acc += po[j] * f;
+                            }
+                    }
+                }
+                out[((size_t)row0 * nq + kvh * G + r) * D + i] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
+            }
+        }
+    }
+}
+
+}  // namespace
+
 // ----------------------------------------------------------------------------- decode, key tiles dealt out evenly
 // The same attention for batches with more (request, head group) pairs than about half the blocks the GPU
 // holds: there, one block per pair (or per fixed split of a pair) leaves a last partial wave of blocks that
@@ -321,7 +416,6 @@ __device__ __forceinline__ void flat_attention(int block, int nblocks, int tid, 
     const int ps_shift = (ps & (ps - 1)) == 0 ? 31 - __clz(ps) : -1;
     const size_t v_off = (size_t)nkv * ps * D, page_stride = 2 * v_off;
     bf16* mine = tiles + warp * DEC_WARP_ELEMS;
-    const int g = lane >> 2, tig = lane & 3;
 
     while (t < t_end) {
         while (prefix[e + 1] * nkv <= t) ++e;  // requests without tiles are stepped over
@@ -483,84 +577,8 @@ __device__ __forceinline__ void flat_attention(int block, int nblocks, int tid, 
         }
         cp_async_wait<0>();
         flat_sync<BAR>();  // every warp is done with its tiles: the space becomes the merge buffer
-        float* mbuf = reinterpret_cast<float*>(tiles);
-        float* wm = mbuf + warp * (32 + 16 * D);  // m[16], l[16], o[16][D]
-        if (tig == 0) {
-            wm[g] = m[0]; wm[g + 8] = m[1];
-            wm[16 + g] = l[0]; wm[16 + g + 8] = l[1];
-        }
-#pragma unroll
-        for (int dt = 0; dt < DTILES; ++dt) {
-            int dim = dt * 8 + tig * 2;
-            wm[32 + g * D + dim] = o[dt][0]; wm[32 + g * D + dim + 1] = o[dt][1];
-            wm[32 + (g + 8) * D + dim] = o[dt][2]; wm[32 + (g + 8) * D + dim + 1] = o[dt][3];
-        }
-        flat_sync<BAR>();
-        const size_t slot = (size_t)block + pair;
-        for (int idx = tid; idx < G * D; idx += DEC_WARPS * 32) {
-            int r = idx / D, i = idx % D;
-            float mx = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < DEC_WARPS; ++w) mx = fmaxf(mx, mbuf[w * (32 + 16 * D) + r]);
-            float lsum = 0.f, acc = 0.f;
-            if (mx > -INFINITY) {
-#pragma unroll
-                for (int w = 0; w < DEC_WARPS; ++w) {
-                    const float* p = mbuf + w * (32 + 16 * D);
-                    float f = fast_exp2(p[r] - mx);
-                    lsum += p[16 + r] * f;
-                    acc += p[32 + r * D + i] * f;
-                }
-            }
-            if (parts == 1) {
-                out[((size_t)row0 * nq + kvh * G + r) * D + i] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
-            } else {
-                part_o[(slot * G + r) * D + i] = acc;
-                if (i == 0) { part_ml[(slot * G + r) * 2] = mx; part_ml[(slot * G + r) * 2 + 1] = lsum; }
-            }
-        }
-        if (parts > 1) {
-            // count this segment in; the last one merges the pair's slots (first_block + pair ... in order)
-            __threadfence();
-            flat_sync<BAR>();
-            if (tid == 0) {
-                int old = atomicAdd(counters + pair, 1);
-                (*s_last) = old == parts - 1;
-                if ((*s_last)) counters[pair] = 0;  // as it was found, for the next launch
-            }
-            flat_sync<BAR>();
-            if ((*s_last)) {
-                __threadfence();
-                const size_t slot0 = (size_t)first_block + pair;
-                for (int idx = tid; idx < G * D; idx += DEC_WARPS * 32) {
-                    int r = idx / D, i = idx % D;
-                    float mx = -INFINITY;
-                    for (int sp = 0; sp < parts; ++sp) mx = fmaxf(mx, __ldcg(part_ml + ((slot0 + sp) * G + r) * 2));
-                    float lsum = 0.f, acc = 0.f;
-                    if (mx > -INFINITY) {
-                        for (int s0 = 0; s0 < parts; s0 += 4) {
-                            float pm[4], pl[4], po[4];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {  // independent loads, in flight together
-                                const bool on = s0 + j < parts;
-                                const size_t sl = slot0 + (on ? s0 + j : 0);
-                                pm[j] = on ? __ldcg(part_ml + (sl * G + r) * 2) : -INFINITY;
-                                pl[j] = on ? __ldcg(part_ml + (sl * G + r) * 2 + 1) : 0.f;
-                                po[j] = on ? __ldcg(part_o + (sl * G + r) * D + i) : 0.f;
-                            }
-#pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                if (s0 + j < parts) {
-                                    float f = fast_exp2(pm[j] - mx);
-                                    lsum += pl[j] * f;
-                                    acc += po[j] * f;
-                                }
-                        }
-                    }
-                    out[((size_t)row0 * nq + kvh * G + r) * D + i] = __float2bfloat16_rn(lsum > 0.f ? acc / lsum : 0.f);
-                }
-            }
-        }
+        decode_segment_finish<BAR, DEC_WARPS>(reinterpret_cast<float*>(tiles), tid, m, l, o, parts, pair, first_block, block, row0, kvh, G,
+                                              nq, out, part_o, part_ml, counters, s_last);
         t += ntiles;
         flat_sync<BAR>();  // the merge buffer and the query tile are free for the next segment
     }

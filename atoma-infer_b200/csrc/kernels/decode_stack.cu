@@ -43,6 +43,7 @@ extern "C" void kernels_set_pdl(int mode) { g_use_pdl = mode; }
 
 namespace {
 
+int g_stack_stream_kv = 1;           // set through decode_stack_set_stream_kv: keys and values through the ring where possible
 int g_stack_inflight = 0;            // set through decode_stack_set_inflight (0: ST_INFLIGHT)
 long long* g_stack_times = nullptr;  // set through decode_stack_set_times: where the next launches leave their clocks
 
@@ -76,12 +77,13 @@ struct alignas(64) StackLayer {
     CUtensorMap map_o;        // [H, nq D], 16 rows
     CUtensorMap map_gate_up;  // [2 I, H], 8 rows
     CUtensorMap map_down;     // [H, I], 16 rows
+    CUtensorMap map_cache;    // this layer's pages as rows of one head's keys (or values) at one slot: [pages * 2 * nkv * page_size, D], boxes of one page
     const float* norm1;       // [H]
     const float* norm2;
     const float* inv_freq;    // [rot / 2]
     bf16* cache;              // this layer's pages
     int store_kv;             // 0: the layer reads another layer's cache and writes nothing
-    int pad[7];
+    int pad[7 + 16];
 };
 static_assert(sizeof(StackLayer) % 64 == 0, "descriptors lie back to back on 64-byte boundaries");
 
@@ -102,7 +104,7 @@ struct StackParams {
     const int* cu_tokens;
     const int* positions;
     int* status;
-    int num_layers, group, M, H, I, nq, nkv, rot, window, num_pages, page_size, S, stages, inflight;
+    int num_layers, group, M, H, I, nq, nkv, rot, window, num_pages, page_size, S, stages, inflight, stream_kv;
     float eps, scale_log2;
     long long* times;           // optional [blocks][layers][10]: the clock after every phase and every barrier (measurements)
 };
@@ -134,6 +136,13 @@ __device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const CUtensorMap
                                                  uint64_t hint) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
                  ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)), "l"(hint) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_to(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_n(uint64_t* bar, uint32_t n) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(n) : "memory");
 }
 // Before the copy engine reads global memory, or writes shared memory, that threads have written or used in the ordinary way.
 __device__ __forceinline__ void fence_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
@@ -181,8 +190,13 @@ __device__ __forceinline__ void stamp(const StackParams& p, int layer, int slot,
 
 // All blocks meet: everything written before it by any block is visible after it to every block.  The block's threads
 // meet first; one of them counts the block in with release semantics (which covers what the others wrote before they
-// met) and polls with acquire semantics; then the threads meet again.
+// met) and polls with acquire semantics; then the threads meet again.  (Without the fence below, a block's own tile of
+// a linear came out as NaN now and then: the copy engine read a row of x that the block's other threads had just
+// written, before it had left the multiprocessor.)
 __device__ __forceinline__ void grid_barrier(const StackParams& p, unsigned long long& target, int tid, const Giveup& gu) {
+    // What this thread wrote in the ordinary way (rows of x in global memory, tiles in shared memory) the copy engine
+    // may read, or overwrite, after the barrier: every writer orders its own writes before the copy engine's accesses.
+    fence_async();
     consumer_sync();
     if (tid == 0) {
         target += gridDim.x;
@@ -201,7 +215,9 @@ __device__ __forceinline__ void grid_barrier(const StackParams& p, unsigned long
 // What a block keeps in shared memory.  Ring, region and the slots of the x ring start on 1,024-byte boundaries (the
 // swizzle of a 128-byte row is a function of address bits 7 to 9).
 struct BlockMem {
+    unsigned char* ring_ptr;  // the ring as a generic pointer
     uint32_t ring;         // weight stages (shared-window addresses)
+    unsigned char* region_ptr;  // the region as a generic pointer
     uint32_t region;       // rows of x for a linear, as [K / 64][rows][64] swizzled; or a ring of x chunks (eight groups
                            // of 64 each); or the attention's query tile and key/value stages
     uint64_t* full;        // [ST_MAX_STAGES] a stage has landed
@@ -232,6 +248,16 @@ __device__ __forceinline__ void rows_to_region(const BlockMem& b, const CUtensor
         fence_async();
         mbar_expect_tx(b.xbar, (uint32_t)rows * (uint32_t)((width + 63) / 64) * 128u);
         tma_load_3d(b.region, map, 0, 0, 0, b.xbar);
+    }
+    // A linear reads x in chunks of eight groups of 64; beyond the last group of the rows the weights' stage holds
+    // zeros, but the region holds whatever was there (a merge buffer of the attention, say), and zero times NaN is
+    // NaN: the rest of the last chunk is zeroed.
+    const int groups = (width + 63) / 64, upto = (groups + 7) / 8 * 8;
+    if (upto > groups) {
+        unsigned char* tail = b.region_ptr + (size_t)groups * rows * 128;
+        for (int i = tid * 16; i < (upto - groups) * rows * 128; i += ST_CONSUMERS * 16)
+            *reinterpret_cast<uint4*>(tail + i) = make_uint4(0u, 0u, 0u, 0u);
+        consumer_sync();
     }
     wait_phase(b.xbar, cur.xuse, gu);
     cur.xuse ^= 1u;
@@ -435,8 +461,267 @@ __device__ __forceinline__ void feed_first_norm(const StackParams& p, const floa
     }
 }
 
+// ----------------------------------------------------------------------------- attention from streamed keys and values
+// With pages of 16 keys, head size 64 and no window, a page's keys (or values) of one head are 16 rows of 128 bytes:
+// one box of the cache's tensor map, landing swizzled the way the tile code reads it.  The stream warp then brings
+// the keys and values too, between the q/k/v weights and the output projection's: the pages of a request are known
+// before the step computes anything (only the newest position's key and value are not in them yet; the segment that
+// owns that position puts them into its tile itself).  A stage holds two 32-key tiles: [K 32 x 64][V 32 x 64] twice.
+// The key tiles of all requests and head groups are dealt out evenly over the blocks as in flat_attention; a block's
+// run is cut into segments at (request, head group) boundaries, a segment's tiles are packed two to a stage, and an
+// arithmetic warp takes whole stages (stage i of the segment goes to warp i mod ST_WARPS).
+// Which keys a block walks.  With at most as many (request, head group) pairs as blocks, every pair is cut into
+// `split` = blocks / pairs parts of equal tile counts and block c takes part c % split of pair c / split: one segment a
+// block (a segment costs about as much in staging the queries and merging as its tiles do, so one larger segment
+// beats two smaller ones of the same total).  With more pairs than blocks, whole pairs are dealt out in turn.
+struct KeySegment {
+    int e, kvh, tile0, ntiles, pair, first_block, parts;
+};
+struct KeyWalk {
+    int pairs, split, next;  // next: the next pair this block takes (pairs: none left)
+};
+__device__ __forceinline__ KeyWalk key_walk(int S, int nkv) {
+    KeyWalk w;
+    w.pairs = S * nkv;
+    w.split = w.pairs <= (int)gridDim.x ? (int)gridDim.x / w.pairs : 0;
+    w.next = w.split ? ((int)blockIdx.x < w.pairs * w.split ? (int)blockIdx.x / w.split : w.pairs) : (int)blockIdx.x;
+    return w;
+}
+// The block's next segment; false: none left.  A segment may be empty (ntiles <= 0) only when false is returned.
+__device__ __forceinline__ bool key_segment(const int* prefix, int nkv, KeyWalk& w, KeySegment& sg) {
+    while (w.next < w.pairs) {
+        const int pair = w.next;
+        w.next = w.split ? w.pairs : pair + (int)gridDim.x;
+        sg.pair = pair;
+        sg.e = pair / nkv;
+        sg.kvh = pair % nkv;
+        const int nt = prefix[sg.e + 1] - prefix[sg.e];
+        if (nt <= 0) continue;  // a padded row of the batch
+        if (w.split) {
+            const int per = (nt + w.split - 1) / w.split, part = (int)blockIdx.x % w.split;
+            sg.tile0 = part * per;
+            sg.ntiles = min(nt, sg.tile0 + per) - sg.tile0;
+            sg.first_block = pair * w.split;
+            sg.parts = (nt + per - 1) / per;
+            if (sg.ntiles <= 0) continue;
+        } else {
+            sg.tile0 = 0;
+            sg.ntiles = nt;
+            sg.first_block = (int)blockIdx.x;
+            sg.parts = 1;
+        }
+        return true;
+    }
+    return false;
+}
+
+// This block's weight stages of the whole launch, in order: which box of which matrix comes next.  (Asking the boxes
+// 16 to 64 stages further on into L2 as well, so that memory keeps working while the ring is full, was measured: the
+// decode step of Llama 3.2 1B at batch 8 went from 1.01 to 1.09-1.13 ms.  The hints compete with the loads the
+// arithmetic warps wait for.)
+struct WeightWalk {
+    int l, phase, tile, c;  // layer, linear of the layer, tile, 512-wide chunk of k
+    unsigned deal;
+    Linear lin;
+    int nchunks;
+    bool done;
+    __device__ __forceinline__ void start(const StackParams& p) {
+        l = 0; phase = -1; tile = 0; c = 0; deal = 0; done = false;
+        lin.tiles = 0; lin.N = lin.K = lin.epi = 0; lin.map = nullptr; nchunks = 0;
+        next_linear(p);
+    }
+    // the first tile of the next linear that has one for this block
+    __device__ __forceinline__ void next_linear(const StackParams& p) {
+        const int ncta = gridDim.x, cta = blockIdx.x;
+        for (;;) {
+            if (phase >= 0) deal += (unsigned)lin.tiles;
+            if (++phase == 4) { phase = 0; ++l; }
+            if (l >= p.num_layers) { done = true; return; }
+            lin = phase_linear(p, p.layers + l, phase);
+            nchunks = (lin.K + ST_KC - 1) / ST_KC;
+            tile = (cta + ncta - (int)(deal % (unsigned)ncta)) % ncta;
+            c = 0;
+            if (tile < lin.tiles) return;
+        }
+    }
+    __device__ __forceinline__ void advance(const StackParams& p) {
+        if (++c < nchunks) return;
+        c = 0;
+        tile += gridDim.x;
+        if (tile >= lin.tiles) next_linear(p);
+    }
+};
+
+// The stream warp's part: this block's key and value pages of one layer into the ring.  All 32 lanes run it: a lane
+// looks up a page, lane 0 counts the bytes in, the lanes ask for their pages.  false: given up.
+__device__ __forceinline__ bool stream_keys(const StackParams& p, const BlockMem& b, const CUtensorMap* cache_map, const int* prefix,
+                                            const int* kvlen, unsigned& count, unsigned& slot, unsigned& free_parity,
+                                            unsigned& gate, unsigned& gate_parity, int lane, const Giveup& gu) {
+    KeyWalk walk = key_walk(p.S, p.nkv);
+    KeySegment sg;
+    while (key_segment(prefix, p.nkv, walk, sg)) {
+        const int lo = sg.tile0 * DEC_KT, hi = min(kvlen[sg.e], (sg.tile0 + sg.ntiles) * DEC_KT);
+        const int page_lo = lo / 16, npages = (hi - lo + 15) / 16;
+        const int* bt = p.meta + p.meta[META_BT_OFFSET + p.group] + (size_t)sg.e * p.meta[META_BT_STRIDE + p.group];
+        for (int pb = 0; pb < npages; pb += 32) {  // 32 pages = 16 tiles = 8 stages a round
+            int page = -1;
+            if (pb + lane < npages) {
+                page = __ldg(bt + page_lo + pb + lane);
+                if (page <= 0 || page >= p.num_pages) {
+                    atomicExch(&p.status[STATUS_BAD_PAGE], 1 + (page_lo + pb + lane) * 16);
+                    page = -1;
+                }
+            }
+            for (int sb = 0; sb < 8 && pb + sb * 4 < npages; ++sb) {
+                const bool mine = (lane >> 2) == sb && page >= 0;
+                const int landing = __popc(__ballot_sync(0xffffffffu, mine));
+                if (!wait_phase(b.empty + slot, free_parity, gu)) return false;
+                if (count >= (unsigned)p.inflight) {
+                    if (!wait_phase(b.full + gate, gate_parity, gu)) return false;
+                    if (++gate == (unsigned)p.stages) { gate = 0; gate_parity ^= 1u; }
+                }
+                if (lane == 0) mbar_expect_tx(b.full + slot, (uint32_t)landing * 2u * 2048u);
+                __syncwarp();
+                if (mine) {  // page q of the stage: tile q / 2, half q % 2; keys, then the values 4 KB further on
+                    const int q = lane & 3;
+                    const uint32_t dst = b.ring + slot * ST_STAGE_BYTES + (uint32_t)(q >> 1) * 8192u + (uint32_t)(q & 1) * 2048u;
+                    tma_load_2d_to(dst, cache_map, 0, ((page * 2 + 0) * p.nkv + sg.kvh) * 16, b.full + slot);
+                    tma_load_2d_to(dst + 4096u, cache_map, 0, ((page * 2 + 1) * p.nkv + sg.kvh) * 16, b.full + slot);
+                }
+                ++count;
+                if (++slot == (unsigned)p.stages) { slot = 0; free_parity ^= 1u; }
+            }
+        }
+    }
+    return true;
+}
+
+// The arithmetic warps' part.  scratch: the region (query tile, the warps' merge buffers, the newest key and value).
+__device__ __forceinline__ void streamed_attention(const StackParams& p, const BlockMem& b, const StackLayer* ly, RingCursor& cur,
+                                                   unsigned char* region, const int* prefix, const int* kvlen, const float2* rope,
+                                                   int* s_last, int tid, const Giveup& gu) {
+    const int lane = tid & 31, warp = tid >> 5;
+    const int nkv = p.nkv, G = p.nq / nkv, q_stride = (p.nq + 2 * nkv) * D;
+    bf16* qtile = reinterpret_cast<bf16*>(region);
+    float* mbuf = reinterpret_cast<float*>(region + 16 * LDS * sizeof(bf16));
+    bf16* newest = reinterpret_cast<bf16*>(mbuf + ST_WARPS * (32 + 16 * D));  // [2][D]: the newest key (rotated) and value
+    const CacheLayout L{nkv, p.page_size, D};
+    KeyWalk walk = key_walk(p.S, nkv);
+    KeySegment sg;
+    unsigned stage0 = 0;  // stages of the phase before the current segment
+    while (key_segment(prefix, nkv, walk, sg)) {
+        const int row0 = p.cu_tokens[sg.e], kv_len = kvlen[sg.e], kvh = sg.kvh;
+        const int lo = sg.tile0 * DEC_KT, hi = min(kv_len, (sg.tile0 + sg.ntiles) * DEC_KT);
+        const bool owner = hi == kv_len;  // this segment holds the newest position
+        const int half = p.rot / 2, pos = kv_len - 1;
+        const bf16* row = p.qkv + (size_t)row0 * q_stride;
+        // ---- the group's queries, rotated, into the tile; the newest key (rotated) and value
+        const float2* cossin = rope + (size_t)sg.e * (D / 2);
+        for (int idx = tid; idx < 16 * (D / 2); idx += ST_CONSUMERS) {
+            const int r = idx / (D / 2), i = idx % (D / 2);
+            if (r < G) {
+                const bf16* x = row + (size_t)(kvh * G + r) * D;
+                if (i < half) {
+                    float a, c;
+                    const float cs = cossin[i].x, sn = cossin[i].y;
+                    rotate_pair(__bfloat162float(__ldcg(x + i)), __bfloat162float(__ldcg(x + i + half)), cs, sn, a, c);
+                    qtile[toff(r, i)] = __float2bfloat16_rn(a);
+                    qtile[toff(r, i + half)] = __float2bfloat16_rn(c);
+                } else {  // dims beyond the rotated part, two to a slot
+                    const int j = p.rot + 2 * (i - half);
+                    qtile[toff(r, j)] = __ldcg(x + j);
+                    qtile[toff(r, j + 1)] = __ldcg(x + j + 1);
+                }
+            } else {
+                qtile[toff(r, 2 * i)] = __float2bfloat16_rn(0.f);
+                qtile[toff(r, 2 * i + 1)] = __float2bfloat16_rn(0.f);
+            }
+        }
+        if (owner) {
+            const bf16* kx = row + (size_t)(p.nq + kvh) * D;
+            const bf16* vx = row + (size_t)(p.nq + nkv + kvh) * D;
+            for (int i = tid; i < half; i += ST_CONSUMERS) {
+                float a, c;
+                const float cs = cossin[i].x, sn = cossin[i].y;
+                rotate_pair(__bfloat162float(__ldcg(kx + i)), __bfloat162float(__ldcg(kx + i + half)), cs, sn, a, c);
+                newest[i] = __float2bfloat16_rn(a);
+                newest[i + half] = __float2bfloat16_rn(c);
+            }
+            for (int i = p.rot + tid; i < D; i += ST_CONSUMERS) newest[i] = __ldcg(kx + i);
+            for (int i = tid; i < D; i += ST_CONSUMERS) newest[D + i] = __ldcg(vx + i);
+        }
+        consumer_sync();
+        if (owner && ly->store_kv) {  // to their page, for the steps to come
+            const int* bt = p.meta + p.meta[META_BT_OFFSET + p.group] + (size_t)sg.e * p.meta[META_BT_STRIDE + p.group];
+            const int page = bt[pos / p.page_size];
+            if (page > 0 && page < p.num_pages) {
+                for (int i = tid; i < 2 * D; i += ST_CONSUMERS)
+                    ly->cache[L.offset(page, i / D, kvh, pos % p.page_size) + (i % D)] = newest[i];
+            } else if (tid == 0) {
+                atomicExch(&p.status[STATUS_BAD_PAGE], 1 + pos);
+            }
+        }
+        uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
+        if (Q_IN_REGS) {
+#pragma unroll
+            for (int ks = 0; ks < KSTEPS; ++ks) load_a_frag(qf[ks], qtile, ks, lane);
+        }
+        float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+        float o[DTILES][4];
+#pragma unroll
+        for (int dt = 0; dt < DTILES; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
+        const int nstages = (sg.ntiles + 1) / 2;
+        for (int si = warp; si < nstages; si += ST_WARPS) {
+            const unsigned n = cur.slot + stage0 + (unsigned)si, slot = n % (unsigned)p.stages;
+            wait_phase(b.full + slot, cur.parity ^ ((n / (unsigned)p.stages) & 1u), gu);
+            unsigned char* st = b.ring_ptr + (size_t)slot * ST_STAGE_BYTES;
+            bool wrote = false;
+            for (int j = 0; j < 2 && si * 2 + j < sg.ntiles; ++j) {
+                bf16* ktile = reinterpret_cast<bf16*>(st + j * 8192);
+                bf16* vtile = ktile + DEC_KT * LDS;
+                const int k0 = lo + (si * 2 + j) * DEC_KT;
+                if (owner && pos >= k0 && pos < k0 + DEC_KT) {  // the tile with the newest position
+                    const int r = pos - k0;  // its row; the rows after it hold nothing: their values must be zeros
+                    for (int i = lane; i < D; i += 32) {
+                        ktile[toff(r, i)] = newest[i];
+                        vtile[toff(r, i)] = newest[D + i];
+                    }
+                    for (int idx = lane; idx < (DEC_KT - 1 - r) * (D / 8); idx += 32) {
+                        const int rr = r + 1 + idx / (D / 8), c8 = (idx % (D / 8)) * 8;
+                        *reinterpret_cast<uint4*>(vtile + toff(rr, c8)) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    wrote = true;
+                    __syncwarp();
+                }
+                float sc[DEC_NK][4];
+                qk_tile<DEC_NK>(sc, qf, qtile, ktile, lane);
+#pragma unroll
+                for (int nn = 0; nn < DEC_NK; ++nn)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int key = k0 + nn * 8 + (lane & 3) * 2 + (c & 1);
+                        sc[nn][c] = key < hi ? sc[nn][c] * p.scale_log2 : -INFINITY;
+                    }
+                softmax_tile<DEC_NK>(sc, m, l, o);
+                pv_tile<DEC_NK>(o, sc, vtile, lane);
+            }
+            __syncwarp();
+            if (wrote) fence_async();  // the copy engine writes this stage next
+            if (lane == 0) mbar_arrive_n(b.empty + slot, ST_WARPS);  // this warp alone used the stage
+        }
+        consumer_sync();  // the queries have been read: their tile and the merge buffer may change
+        decode_segment_finish<BAR_CONSUMERS, ST_WARPS>(mbuf, tid, m, l, o, sg.parts, sg.pair, sg.first_block, (int)blockIdx.x, row0, kvh, G, p.nq,
+                                                       p.attn_out, p.part_o, p.part_ml, p.counters, s_last);
+        stage0 += (unsigned)nstages;
+        consumer_sync();
+    }
+    const unsigned n = cur.slot + stage0;
+    cur.parity ^= (n / (unsigned)p.stages) & 1u;
+    cur.slot = n % (unsigned)p.stages;
+}
+
 size_t stack_region_bytes(int M, int xwidth) {
-    const size_t rows_bytes = (size_t)(M <= 8 ? 8 : 16) * (size_t)((xwidth + 63) / 64) * 128;
+    const size_t rows_bytes = (size_t)(M <= 8 ? 8 : 16) * (size_t)(((xwidth + 63) / 64 + 7) / 8 * 8) * 128;  // whole chunks of eight groups
     return ((rows_bytes > DEC_MAIN_BYTES ? rows_bytes : DEC_MAIN_BYTES) + 1023) / 1024 * 1024;
 }
 
@@ -448,8 +733,10 @@ decode_stack_kernel(const StackParams p, const __grid_constant__ CUtensorMap map
     const int rows = p.M <= 8 ? 8 : 16;
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     BlockMem b;
+    b.ring_ptr = smem;
     b.ring = smem_u32(smem);
     unsigned char* region = smem + (size_t)p.stages * ST_STAGE_BYTES;
+    b.region_ptr = region;
     b.region = smem_u32(region);
     b.redbuf = reinterpret_cast<float*>(region + region_bytes);
     const int red_floats = 2 * ST_WARPS * 16 * (rows + 1);
@@ -460,8 +747,10 @@ decode_stack_kernel(const StackParams p, const __grid_constant__ CUtensorMap map
     b.xempty = b.xfull + ST_XRING;
     b.xbar = b.xempty + ST_XRING;
     int* prefix = reinterpret_cast<int*>(b.xbar + 1);  // [ST_MAX_ROWS + 1]
-    int* s_last = prefix + ST_MAX_ROWS + 1;
+    int* kvlen = prefix + ST_MAX_ROWS + 1;             // [ST_MAX_ROWS] keys of every request, the newest included
+    int* s_last = kvlen + ST_MAX_ROWS;
     volatile int* gave_up = s_last + 1;
+    float2* rope = reinterpret_cast<float2*>(s_last + 3);  // [ST_MAX_ROWS][D / 2] (cos, sin) of the requests' newest positions
     b.xdepth = region_bytes / (rows * 1024);
     if (b.xdepth > ST_XRING) b.xdepth = ST_XRING;
     const Giveup gu{gave_up, p.status, 1 + (int)blockIdx.x};
@@ -482,48 +771,49 @@ decode_stack_kernel(const StackParams p, const __grid_constant__ CUtensorMap map
     __syncthreads();
 
     if (warp == ST_WARPS) {
-        // ---- the weight stream: this block's tiles of every linear of every layer, in order; one lane does it all
-        if (lane == 0) {
-            uint64_t policy;
-            asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
-            unsigned count = 0, deal = 0;
-            unsigned slot = 0, free_parity = 1u;  // the stage that comes next, the parity of its "free" phase
-            unsigned gate = 0, gate_parity = 0u;  // the stage `inflight` before it, the parity of its "landed" phase
-            const int ncta = gridDim.x, cta = blockIdx.x;
-            bool on = true;
-            for (int l = 0; l < p.num_layers && on; ++l) {
-                for (int phase = 0; phase < 4 && on; ++phase) {
-                    const Linear lin = phase_linear(p, p.layers + l, phase);
-                    const int n_out = lin.epi == 1 ? lin.N / 2 : lin.N;
-                    const int nchunks = (lin.K + ST_KC - 1) / ST_KC;
-                    const int first = (cta + ncta - (int)(deal % (unsigned)ncta)) % ncta;
-                    for (int tile = first; tile < lin.tiles && on; tile += ncta) {
-                        for (int c = 0; c < nchunks; ++c) {
-                            if (!wait_phase(b.empty + slot, free_parity, gu)) { on = false; break; }
-                            if (count >= (unsigned)p.inflight) {  // not too much on its way at once
-                                if (!wait_phase(b.full + gate, gate_parity, gu)) { on = false; break; }
-                                if (++gate == (unsigned)p.stages) { gate = 0; gate_parity ^= 1u; }
-                            }
-                            const uint32_t dst = b.ring + slot * ST_STAGE_BYTES;
-                            mbar_expect_tx(b.full + slot, (uint32_t)ST_STAGE_BYTES);  // rows and k beyond the matrix arrive as zeros
-                            if (lin.epi == 1) {
-                                tma_load_3d_hint(dst, lin.map, 0, tile * 8, c * (ST_KC / 64), b.full + slot, policy);
-                                tma_load_3d_hint(dst + ST_STAGE_BYTES / 2, lin.map, 0, n_out + tile * 8, c * (ST_KC / 64), b.full + slot, policy);
-                            } else {
-                                tma_load_3d_hint(dst, lin.map, 0, tile * 16, c * (ST_KC / 64), b.full + slot, policy);
-                            }
-                            ++count;
-                            if (++slot == (unsigned)p.stages) { slot = 0; free_parity ^= 1u; }
-                        }
-                    }
-                    deal += (unsigned)lin.tiles;
+        // ---- the stream: this block's tiles of every linear of every layer, in order, and between a layer's q/k/v
+        // and output projections its share of the layer's keys and values; lane 0 asks for the weights
+        asm volatile("bar.sync %0, %1;" ::"n"(BAR_ALL), "n"(ST_THREADS) : "memory");  // the tile counts of the requests are there
+        uint64_t policy;
+        asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+        unsigned count = 0;
+        unsigned slot = 0, free_parity = 1u;  // the stage that comes next, the parity of its "free" phase
+        unsigned gate = 0, gate_parity = 0u;  // the stage `inflight` before it, the parity of its "landed" phase
+        WeightWalk at;                         // what the ring gets next
+        at.start(p);
+        int kv_next = 0;                       // the first layer whose keys and values have not been asked for yet
+        bool on = true;
+        while (on) {
+            // a layer's keys and values come after this block's stages of its q/k/v matrix and before any later stage
+            while (p.stream_kv && on && kv_next < p.num_layers && (at.done || 4 * kv_next < 4 * at.l + at.phase)) {
+                on = stream_keys(p, b, &p.layers[kv_next].map_cache, prefix, kvlen, count, slot, free_parity, gate, gate_parity, lane, gu);
+                ++kv_next;
+            }
+            if (at.done || !on) break;
+            if (!wait_phase(b.empty + slot, free_parity, gu)) { on = false; break; }
+            if (count >= (unsigned)p.inflight) {  // not too much on its way at once
+                if (!wait_phase(b.full + gate, gate_parity, gu)) { on = false; break; }
+                if (++gate == (unsigned)p.stages) { gate = 0; gate_parity ^= 1u; }
+            }
+            if (lane == 0) {
+                const uint32_t dst = b.ring + slot * ST_STAGE_BYTES;
+                const int k0 = at.c * (ST_KC / 64);
+                mbar_expect_tx(b.full + slot, (uint32_t)ST_STAGE_BYTES);  // rows and k beyond the matrix arrive as zeros
+                if (at.lin.epi == 1) {
+                    tma_load_3d_hint(dst, at.lin.map, 0, at.tile * 8, k0, b.full + slot, policy);
+                    tma_load_3d_hint(dst + ST_STAGE_BYTES / 2, at.lin.map, 0, at.lin.N / 2 + at.tile * 8, k0, b.full + slot, policy);
+                } else {
+                    tma_load_3d_hint(dst, at.lin.map, 0, at.tile * 16, k0, b.full + slot, policy);
                 }
             }
-            // nothing this lane asked for may still be on its way when the block leaves
-            const unsigned issued = count, back = issued < (unsigned)p.stages ? issued : (unsigned)p.stages;
-            for (unsigned i = issued - back; i < issued; ++i)
-                wait_phase(b.full + i % (unsigned)p.stages, (i / (unsigned)p.stages) & 1u, gu, false);
+            ++count;
+            if (++slot == (unsigned)p.stages) { slot = 0; free_parity ^= 1u; }
+            at.advance(p);
         }
+        // nothing this warp asked for may still be on its way when the block leaves
+        const unsigned issued = count, back = issued < (unsigned)p.stages ? issued : (unsigned)p.stages;
+        for (unsigned i = issued - back; i < issued; ++i)
+            wait_phase(b.full + i % (unsigned)p.stages, (i / (unsigned)p.stages) & 1u, gu, false);
     } else {
         // ---- the arithmetic
         const int NT = p.M <= 8 ? 1 : 2;
@@ -536,6 +826,8 @@ decode_stack_kernel(const StackParams p, const __grid_constant__ CUtensorMap map
             target = ld_acquire(p.arrivals) / per_launch * per_launch;  // what it was when the launch began
         }
         if (warp < DEC_WARPS) flat_prefix<BAR_ATTENTION>(prefix, p.meta, p.cu_tokens, p.positions, p.S, p.window, tid);
+        if (tid < ST_MAX_ROWS) kvlen[tid] = tid < min(p.S, p.meta[META_NUM_ENTRIES]) ? p.positions[p.cu_tokens[tid]] + 1 : 0;
+        asm volatile("bar.sync %0, %1;" ::"n"(BAR_ALL), "n"(ST_THREADS) : "memory");  // the stream warp reads them
         RingCursor cur{0u, 0u, 0u, 0u, 0u, 0u, 0u, 1u, 0u};
         const int q_stride = (p.nq + 2 * p.nkv) * D;
         const int hidden_tiles = (p.H + 15) / 16;
@@ -543,6 +835,7 @@ decode_stack_kernel(const StackParams p, const __grid_constant__ CUtensorMap map
         feed_first_norm(p, p.layers[0].norm1, b.redbuf, tid);
         grid_barrier(p, target, tid, gu);
         int np = 1;  // blocks that left a share of the rows' sums of squares
+        const float* rope_of = nullptr;  // the frequencies the (cos, sin) table was made from
         for (int l = 0; l < p.num_layers; ++l) {
             const StackLayer* ly = p.layers + l;
             // 1. the normed rows (their scale applied to the products), q/k/v
@@ -555,7 +848,22 @@ decode_stack_kernel(const StackParams p, const __grid_constant__ CUtensorMap map
             grid_barrier(p, target, tid, gu);
             stamp(p, l, 1, tid);
             // 2. attention
-            if (warp < DEC_WARPS)
+            if (p.stream_kv)
+                {
+                if (ly->inv_freq != rope_of) {  // (cos, sin) of every request's newest position; the same for all layers, as a rule
+                    consumer_sync();
+                    for (int idx = tid; idx < p.S * (p.rot / 2); idx += ST_CONSUMERS) {
+                        const int e = idx / (p.rot / 2), i = idx % (p.rot / 2);
+                        float sn, cs;
+                        sincosf((float)(kvlen[e] - 1) * ly->inv_freq[i], &sn, &cs);
+                        rope[e * (D / 2) + i] = make_float2(cs, sn);
+                    }
+                    rope_of = ly->inv_freq;
+                    consumer_sync();
+                }
+                streamed_attention(p, b, ly, cur, region, prefix, kvlen, rope, s_last, tid, gu);
+            }
+            else if (warp < DEC_WARPS)
                 flat_attention<BAR_ATTENTION>(blockIdx.x, gridDim.x, tid, qtile, tiles, prefix, s_last, p.qkv, q_stride, ly->cache, L, p.meta,
                                               p.group, p.cu_tokens, p.positions, p.attn_out, p.part_o, p.part_ml, p.counters, ly->inv_freq,
                                               p.rot, ly->store_kv, p.nq, p.window, p.scale_log2, p.num_pages, p.S, p.status);
@@ -631,10 +939,27 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, long long K, i
     return true;
 }
 
+// A layer's pages [pages, 2, nkv, 16, 64] as rows of 64: one box is a page's keys (or values) of one head.
+bool make_cache_map(CUtensorMap* map, const void* base, long long rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn || rows <= 0 || ((uintptr_t)base & 15)) return false;
+    alignas(64) CUtensorMap tmp;
+    cuuint64_t dims[2] = {64, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {128};
+    cuuint32_t box[2] = {64, 16};
+    cuuint32_t estr[2] = {1, 1};
+    if (fn(&tmp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    memcpy(map, &tmp, sizeof(tmp));
+    return true;
+}
+
 size_t stack_fixed_smem(int M, int xwidth) {
     const size_t red = (size_t)((2 * ST_WARPS * 16 * ((M <= 8 ? 8 : 16) + 1) + 3) / 4) * 4 * sizeof(float);
     return stack_region_bytes(M, xwidth) + red + ST_MAX_ROWS * sizeof(float) + (2 * ST_MAX_STAGES + 2 * ST_XRING + 1) * sizeof(uint64_t) +
-           (ST_MAX_ROWS + 1 + 2) * sizeof(int) + 1024 + 64;
+           (2 * ST_MAX_ROWS + 1 + 2) * sizeof(int) + ST_MAX_ROWS * (D / 2) * sizeof(float2) + 1024 + 64;
 }
 
 struct StackPlan { int blocks, stages; size_t smem; };
@@ -672,21 +997,27 @@ extern "C" int decode_stack_max_rows() { return ST_MAX_ROWS; }
 
 // Writes one layer's descriptor (decode_stack_layer_bytes() bytes, host memory; the table of all layers then goes to
 // the device, which must keep it on a 64-byte boundary).  Weights are bfloat16, row-major: w_qkv [(nq + 2 nkv) D, H],
-// w_o [H, nq D], w_gate_up [2 I, H] (gate rows, then up rows), w_down [H, I]; H, nq D and I multiples of 64.
+// w_o [H, nq D], w_gate_up [2 I, H] (gate rows, then up rows), w_down [H, I]; H, nq D and I multiples of 64.  cache:
+// the layer's pages [num_pages, 2, nkv, page_size, D].
 // 0, or an error (the widths, or a tensor map the driver refused).
 extern "C" int decode_stack_fill_layer(void* dst, const void* w_qkv, const void* w_o, const void* w_gate_up, const void* w_down,
                                        const float* norm1, const float* norm2, const float* inv_freq, void* cache, int store_kv,
-                                       int H, int I, int nq, int nkv) {
+                                       int H, int I, int nq, int nkv, int page_size, int num_pages) {
     StackLayer ly;
     memset(&ly, 0, sizeof(ly));
     if (H % 64 || I % 64 || (nq * D) % 64) return (int)cudaErrorInvalidValue;
     if (!make_map(&ly.map_qkv, w_qkv, (long long)(nq + 2 * nkv) * D, H, 16, ST_KC / 64) || !make_map(&ly.map_o, w_o, H, (long long)nq * D, 16, ST_KC / 64) ||
         !make_map(&ly.map_gate_up, w_gate_up, 2ll * I, H, 8, ST_KC / 64) || !make_map(&ly.map_down, w_down, H, I, 16, ST_KC / 64))
         return (int)cudaErrorInvalidValue;
+    if (D == 64 && page_size == 16 && !make_cache_map(&ly.map_cache, cache, (long long)num_pages * 2 * nkv * 16)) return (int)cudaErrorInvalidValue;
     ly.norm1 = norm1; ly.norm2 = norm2; ly.inv_freq = inv_freq; ly.cache = (bf16*)cache; ly.store_kv = store_kv;
     memcpy(dst, &ly, sizeof(ly));
     return 0;
 }
+
+// For tests and measurements: 0 = the attention fetches keys and values itself (the only way with a window, a head
+// size other than 64 or pages other than 16), 1 (the default) = the stream warp brings them where it can.
+extern "C" void decode_stack_set_stream_kv(int on) { g_stack_stream_kv = on; }
 
 // For measurements: how many stages a block may have on their way at once (0: the default).
 extern "C" void decode_stack_set_inflight(int stages) { g_stack_inflight = stages; }
@@ -709,12 +1040,14 @@ extern "C" size_t decode_stack_scratch_floats(int S, int nq, int nkv, int blocks
 // rows of a decode step.  resid [M, H] float32 is updated in place; delta (optional, bfloat16 [M, H]) is added to it
 // on the way.  qkv, attn_out, act, xw ([M, H]): bfloat16 workspaces of M rows, 16-byte aligned; ss_part:
 // ceil(H / 16) * 16 floats; scratch: decode_stack_scratch_floats(...) floats; counters: S * nkv ints, zero (left zero);
-// arrivals: one 64-bit counter that belongs to this (layers, device) pair alone and starts at zero.
+// arrivals: one 64-bit counter that belongs to this (layers, device) pair alone and starts at zero.  all_store_kv: every
+// layer writes its own cache (a layer that reads another layer's pages needs what that layer wrote a moment ago, which
+// a stream that runs ahead may miss: the attention then fetches keys and values itself).
 extern "C" int decode_stack(const void* layers, int num_layers, void* resid, const void* delta, void* qkv, void* attn_out,
                             void* act, void* xw, float* ss_part, float* scratch, int* counters, unsigned long long* arrivals,
                             const int* meta, int group, const int* cu_tokens, const int* positions, int M, int S, int H, int I,
                             int nq, int nkv, int rot, int window, int page_size, int num_pages, float eps, float scale,
-                            int* status, cudaStream_t stream) {
+                            int all_store_kv, int* status, cudaStream_t stream) {
     if (num_layers <= 0 || M <= 0) return 0;
     if (M > ST_MAX_ROWS || S != M || H % 64 || I % 64 || (nq * D) % 64 || nq % nkv || nq / nkv > 16 || rot % 2 || rot > D || rot <= 0 ||
         ((uintptr_t)layers & 63))
@@ -750,6 +1083,7 @@ extern "C" int decode_stack(const void* layers, int num_layers, void* resid, con
     p.window = window; p.num_pages = num_pages; p.page_size = page_size; p.S = S; p.stages = plan.stages;
     p.eps = eps; p.scale_log2 = scale * LOG2E;
     p.times = g_stack_times;
+    p.stream_kv = (g_stack_stream_kv && all_store_kv && D == 64 && page_size == 16 && window == 0) ? 1 : 0;
     p.inflight = g_stack_inflight > 0 ? g_stack_inflight : ST_INFLIGHT;
     if (p.inflight > p.stages) p.inflight = p.stages;
     const int region_bytes = (int)stack_region_bytes(M, xwidth);

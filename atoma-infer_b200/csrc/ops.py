@@ -338,7 +338,8 @@ class CudaOps:
             self._stack_libs[d] = lib
         return lib
 
-    def decode_stack_layers(self, layers, *, d: int, hidden: int, intermediate: int, nq: int, nkv: int) -> torch.Tensor:
+    def decode_stack_layers(self, layers, *, d: int, hidden: int, intermediate: int, nq: int, nkv: int, page_size: int,
+                            num_pages: int) -> torch.Tensor:
         """The layer kernel's descriptors on the device, one per dict of ``layers`` (tensors ``w_qkv``, ``w_o``,
         ``w_gate_up``, ``w_down``, ``norm1``, ``norm2``, ``inv_freq``, ``cache``; bool ``store_kv``)."""
         lib = self._decode_stack_library(d)
@@ -348,7 +349,7 @@ class CudaOps:
             err = lib.decode_stack_fill_layer(ctypes.c_void_p(host.data_ptr() + i * size), _p(ly["w_qkv"]), _p(ly["w_o"]),
                                               _p(ly["w_gate_up"]), _p(ly["w_down"]), _p(ly["norm1"]), _p(ly["norm2"]),
                                               _p(ly["inv_freq"]), _p(ly["cache"]), int(ly["store_kv"]), hidden, intermediate,
-                                              nq, nkv)
+                                              nq, nkv, page_size, num_pages)
             if err:
                 raise KernelError(f"decode_stack_fill_layer: error {err} (widths must be multiples of 64)")
         return host.to(self.device)
@@ -365,7 +366,7 @@ class CudaOps:
 
     def decode_stack(self, layers, num_layers: int, resid, delta, arrivals, ctx, group: int, *, hidden: int, intermediate: int,
                      nq: int, nkv: int, d: int, rot: int, window: int, page_size: int, num_pages: int, eps: float,
-                     scale: float):
+                     scale: float, all_store_kv: bool = True):
         """``num_layers`` pre-norm layers (RMSNorm, rotary attention over the paged cache, SwiGLU) of a decode step in
         one launch (kernels/decode_stack.cu): resid [rows, hidden] float32 is updated in place, ``delta`` added first."""
         lib = self._decode_stack_library(d)
@@ -385,7 +386,7 @@ class CudaOps:
         self._check(lib.decode_stack(_p(layers), num_layers, _p(resid), _p(delta), _p(qkv), _p(out), _p(act), _p(xw), _p(ss_part), _p(scratch),
                                      _p(self._counters), _p(arrivals), _p(ctx.meta), group, _p(ctx.cu_tokens), _p(ctx.positions),
                                      M, ctx.S, hidden, intermediate, nq, nkv, rot, window, page_size, num_pages,
-                                     ctypes.c_float(eps), ctypes.c_float(scale), _p(self.status), self._stream()),
+                                     ctypes.c_float(eps), ctypes.c_float(scale), int(all_store_kv), _p(self.status), self._stream()),
                     "decode_stack")
 
     def _decode_flat_blocks(self, lib, d: int, S: int, nkv: int) -> int:

@@ -61,7 +61,8 @@ class DecodeStack:
                                    cache=v.pages, store_kv=bool(v.writes)))
             self._table = self.rt.ops.decode_stack_layers(layers, d=self.head_dim, hidden=self.hidden,
                                                           intermediate=self.intermediate, nq=self.num_heads,
-                                                          nkv=self.num_kv_heads)
+                                                          nkv=self.num_kv_heads, page_size=views[0].page_size,
+                                                          num_pages=views[0].num_pages)
             self._table_key = key
         return self._table
 
@@ -71,7 +72,8 @@ class DecodeStack:
         self.rt.ops.decode_stack(self._layer_table(views), len(self.fusions), resid, delta, self.arrivals, ctx, self.group,
                                  hidden=self.hidden, intermediate=self.intermediate, nq=self.num_heads, nkv=self.num_kv_heads,
                                  d=self.head_dim, rot=self.rotary_dim, window=self.window, page_size=v0.page_size,
-                                 num_pages=v0.num_pages, eps=self.eps, scale=self.scale)
+                                 num_pages=v0.num_pages, eps=self.eps, scale=self.scale,
+                                 all_store_kv=all(v.writes for v in views))
 
 
 def plan_stacks(blocks, runs, run_owner, run_group, rt) -> Dict[int, DecodeStack]:
