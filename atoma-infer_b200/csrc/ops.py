@@ -354,6 +354,12 @@ class CudaOps:
                 raise KernelError(f"decode_stack_fill_layer: error {err} (widths must be multiples of 64)")
         return host.to(self.device)
 
+    def decode_stack_record_clocks(self, d: int, buffer: Optional[torch.Tensor]) -> None:
+        """For measurements: the next launches of the layer kernel leave the global clock after every phase and every
+        barrier of every layer in ``buffer`` (int64 [blocks, layers, 10]; None: off).  Reading that clock costs each
+        block a few hundred nanoseconds a time."""
+        self._decode_stack_library(d).decode_stack_set_times(_p(buffer))
+
     def decode_stack_blocks(self, d: int, rows: int, hidden: int) -> int:
         """Blocks the layer kernel would run with for ``rows`` rows of width ``hidden`` (the larger of the model's
         width and heads x head size; 0: it does not take them)."""

@@ -157,6 +157,45 @@ def serving_workload(which: str) -> int:
     return 0
 
 
+def layer_kernel_phases(eng, args, prompt, greedy, cfg) -> int:
+    """Decode steps through the persistent layer kernel (csrc/kernels/decode_stack.cu), eagerly, with every block
+    writing the global clock after each phase and each barrier of each layer; prints the mean, the slowest and the
+    fastest block per slot.  The clock reads themselves cost about 0.3 us a slot."""
+    import torch
+
+    lm, ops = eng.lm, eng.lm.rt.ops
+    ops.fused_layers = True
+    lm.step.cuda_graphs = False
+    d, H, L = cfg["head_dim"], cfg["hidden_size"], cfg["num_hidden_layers"]
+    ids = [eng.add_request(prompt(), greedy) for _ in range(args.batch)]
+    while any(eng.scheduler.num_computed(i) < args.context for i in ids):
+        eng.step()
+    for _ in range(max(args.warmup, 3)):
+        eng.step()
+    blocks = ops.decode_stack_blocks(d, args.batch, max(H, cfg["num_attention_heads"] * d))
+    if not blocks:
+        print("the layer kernel does not take this geometry")
+        return 1
+    clocks = torch.zeros((blocks, L, 10), dtype=torch.int64, device=lm.rt.device)
+    ops.decode_stack_record_clocks(d, clocks)
+    for _ in range(3):
+        eng.step()
+    torch.cuda.synchronize()
+    ops.decode_stack_record_clocks(d, None)
+    t = clocks.cpu().double()
+    begin = torch.cat([t[:, :-1, 9:10], t[:, 1:, :9]], dim=2)  # a slot begins where the one before it ended
+    dur = (t[:, 1:, :] - begin) / 1000.0                      # us; layers 1 .. L-1
+    names = ["norm scales + q/k/v", "barrier", "attention", "barrier", "output projection", "barrier",
+             "norm scales + gate/up", "barrier", "down projection", "barrier"]
+    print(f"layer kernel, batch {args.batch}, context {args.context}, {L} layers, {blocks} blocks: us per slot "
+          f"(mean over blocks and layers | slowest block | fastest block)")
+    for j, name in enumerate(names):
+        per_block = dur[:, :, j].mean(1)
+        print(f"  {name:24s} {dur[:, :, j].mean().item():6.2f} | {per_block.max().item():6.2f} | {per_block.min().item():6.2f}")
+    print(f"  a layer (block 0): {((t[0, -1, 9] - t[0, 0, 9]) / 1000.0 / (L - 1)).item():.2f} us")
+    return 0
+
+
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.isfile(p):
@@ -216,6 +255,9 @@ def main() -> int:
     ap.add_argument("--context", type=int, default=PROMPT_LEN,
                     help="prompt length of the decode measurements (default 2,048; 8,192 and 32,768 for long contexts)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points")
+    ap.add_argument("--layer-kernel-phases", action="store_true",
+                    help="instead of the benchmark: decode steps with the persistent layer kernel switched on, and the "
+                         "time its blocks spend in every phase and at every barrier of a layer (a table, for profiles/)")
     ap.add_argument("--phase", default="all", choices=["all", "prefill", "decode"],
                     help="measure only one phase (for profiling); the JSON line then lacks the other")
     args = ap.parse_args()
@@ -275,6 +317,9 @@ def main() -> int:
         b.record()
         torch.cuda.synchronize()
         return a.elapsed_time(b)
+
+    if args.layer_kernel_phases:
+        return layer_kernel_phases(eng, args, prompt, greedy, cfg)
 
     # ------------------------------------------------------------------ prefill of 2,048 tokens
     toks = torch.randint(0, V, (PREFILL_TOKENS,), generator=g).tolist()
