@@ -44,6 +44,7 @@ extern "C" void kernels_set_pdl(int mode) { g_use_pdl = mode; }
 namespace {
 
 int g_stack_stream_kv = 1;           // set through decode_stack_set_stream_kv: keys and values through the ring where possible
+int g_stack_max_split = 1 << 20;     // set through decode_stack_set_max_split
 int g_stack_inflight = 0;            // set through decode_stack_set_inflight (0: ST_INFLIGHT)
 long long* g_stack_times = nullptr;  // set through decode_stack_set_times: where the next launches leave their clocks
 
@@ -104,7 +105,7 @@ struct StackParams {
     const int* cu_tokens;
     const int* positions;
     int* status;
-    int num_layers, group, M, H, I, nq, nkv, rot, window, num_pages, page_size, S, stages, inflight, stream_kv;
+    int num_layers, group, M, H, I, nq, nkv, rot, window, num_pages, page_size, S, stages, inflight, stream_kv, max_split;
     float eps, scale_log2;
     long long* times;           // optional [blocks][layers][10]: the clock after every phase and every barrier (measurements)
 };
@@ -480,10 +481,10 @@ struct KeySegment {
 struct KeyWalk {
     int pairs, split, next;  // next: the next pair this block takes (pairs: none left)
 };
-__device__ __forceinline__ KeyWalk key_walk(int S, int nkv) {
+__device__ __forceinline__ KeyWalk key_walk(int S, int nkv, int max_split) {
     KeyWalk w;
     w.pairs = S * nkv;
-    w.split = w.pairs <= (int)gridDim.x ? (int)gridDim.x / w.pairs : 0;
+    w.split = w.pairs <= (int)gridDim.x ? min((int)gridDim.x / w.pairs, max_split) : 0;
     w.next = w.split ? ((int)blockIdx.x < w.pairs * w.split ? (int)blockIdx.x / w.split : w.pairs) : (int)blockIdx.x;
     return w;
 }
@@ -557,7 +558,7 @@ struct WeightWalk {
 __device__ __forceinline__ bool stream_keys(const StackParams& p, const BlockMem& b, const CUtensorMap* cache_map, const int* prefix,
                                             const int* kvlen, unsigned& count, unsigned& slot, unsigned& free_parity,
                                             unsigned& gate, unsigned& gate_parity, int lane, const Giveup& gu) {
-    KeyWalk walk = key_walk(p.S, p.nkv);
+    KeyWalk walk = key_walk(p.S, p.nkv, p.max_split);
     KeySegment sg;
     while (key_segment(prefix, p.nkv, walk, sg)) {
         const int lo = sg.tile0 * DEC_KT, hi = min(kvlen[sg.e], (sg.tile0 + sg.ntiles) * DEC_KT);
@@ -606,7 +607,7 @@ __device__ __forceinline__ void streamed_attention(const StackParams& p, const B
     float* mbuf = reinterpret_cast<float*>(region + 16 * LDS * sizeof(bf16));
     bf16* newest = reinterpret_cast<bf16*>(mbuf + ST_WARPS * (32 + 16 * D));  // [2][D]: the newest key (rotated) and value
     const CacheLayout L{nkv, p.page_size, D};
-    KeyWalk walk = key_walk(p.S, nkv);
+    KeyWalk walk = key_walk(p.S, nkv, p.max_split);
     KeySegment sg;
     unsigned stage0 = 0;  // stages of the phase before the current segment
     while (key_segment(prefix, nkv, walk, sg)) {
@@ -1019,6 +1020,11 @@ extern "C" int decode_stack_fill_layer(void* dst, const void* w_qkv, const void*
 // size other than 64 or pages other than 16), 1 (the default) = the stream warp brings them where it can.
 extern "C" void decode_stack_set_stream_kv(int on) { g_stack_stream_kv = on; }
 
+// For measurements: the most parts a (request, head group) pair is cut into (one part a pair at batch 8, 64 blocks
+// walking 65 tiles each: the slowest block 21 us instead of 15; a block brings keys and values as 2 KB boxes, which
+// the copy engine starts at about one per 80 cycles, 30 to 40 GB/s a block).
+extern "C" void decode_stack_set_max_split(int parts) { g_stack_max_split = parts > 0 ? parts : 1; }
+
 // For measurements: how many stages a block may have on their way at once (0: the default).
 extern "C" void decode_stack_set_inflight(int stages) { g_stack_inflight = stages; }
 
@@ -1083,6 +1089,7 @@ extern "C" int decode_stack(const void* layers, int num_layers, void* resid, con
     p.window = window; p.num_pages = num_pages; p.page_size = page_size; p.S = S; p.stages = plan.stages;
     p.eps = eps; p.scale_log2 = scale * LOG2E;
     p.times = g_stack_times;
+    p.max_split = g_stack_max_split;
     p.stream_kv = (g_stack_stream_kv && all_store_kv && D == 64 && page_size == 16 && window == 0) ? 1 : 0;
     p.inflight = g_stack_inflight > 0 ? g_stack_inflight : ST_INFLIGHT;
     if (p.inflight > p.stages) p.inflight = p.stages;
