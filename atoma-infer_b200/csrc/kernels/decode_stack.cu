@@ -51,8 +51,11 @@ long long* g_stack_times = nullptr;  // set through decode_stack_set_times: wher
 // Arithmetic warps.  Eight (two a scheduler, which hides the latencies of a stage's loads and multiply-adds behind
 // each other) where the attention's registers allow it: with the stream warp that is 288 threads and at most 168
 // registers a thread, which the walk over the keys fits into up to head size 64.  Larger heads: four (255 registers).
-// The first four (DEC_WARPS) walk the keys.
+// (Eight at head size 128, with the query fragments read from shared memory for every tile, still spilt 400 bytes:
+// the linears got slower, gate/up at Llama 3.1 8B sizes 42 -> 48 us, and the attention no faster.)
+// The first four (DEC_WARPS) walk the keys when the stream cannot bring them.
 constexpr int ST_WARPS = D <= 64 ? 8 : 4;
+constexpr bool ST_Q_IN_REGS = Q_IN_REGS;
 constexpr int ST_KB = 16 / ST_WARPS;           // 32-wide k blocks of a stage per warp
 constexpr int ST_CONSUMERS = ST_WARPS * 32;
 constexpr int ST_THREADS = ST_CONSUMERS + 32;  // and the warp that streams weights
@@ -78,7 +81,7 @@ struct alignas(64) StackLayer {
     CUtensorMap map_o;        // [H, nq D], 16 rows
     CUtensorMap map_gate_up;  // [2 I, H], 8 rows
     CUtensorMap map_down;     // [H, I], 16 rows
-    CUtensorMap map_cache;    // this layer's pages as rows of one head's keys (or values) at one slot: [pages * 2 * nkv * page_size, D], boxes of one page
+    CUtensorMap map_cache;    // this layer's pages as rows of one head's keys (or values) at one slot, [pages * 2 * nkv * page_size][D] in 64-wide column blocks; a box is one page of one head
     const float* norm1;       // [H]
     const float* norm2;
     const float* inv_freq;    // [rot / 2]
@@ -137,10 +140,6 @@ __device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const CUtensorMap
                                                  uint64_t hint) {
     asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
                  ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar)), "l"(hint) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d_to(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive_n(uint64_t* bar, uint32_t n) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(n) : "memory");
@@ -463,11 +462,62 @@ __device__ __forceinline__ void feed_first_norm(const StackParams& p, const floa
 }
 
 // ----------------------------------------------------------------------------- attention from streamed keys and values
-// With pages of 16 keys, head size 64 and no window, a page's keys (or values) of one head are 16 rows of 128 bytes:
-// one box of the cache's tensor map, landing swizzled the way the tile code reads it.  The stream warp then brings
-// the keys and values too, between the q/k/v weights and the output projection's: the pages of a request are known
-// before the step computes anything (only the newest position's key and value are not in them yet; the segment that
-// owns that position puts them into its tile itself).  A stage holds two 32-key tiles: [K 32 x 64][V 32 x 64] twice.
+// With pages of 16 keys, head size 64 or 128 and no window, a page's keys (or values) of one head come as one box of
+// the cache's tensor map: 16 rows, in 64-wide column blocks of [16][64] (one block at head size 64, two at 128), each
+// 128-byte swizzled.  The stream warp then brings the keys and values too, between the q/k/v weights and the output
+// projection's: the pages of a request are known before the step computes anything (only the newest position's key
+// and value are not in them yet; the segment that owns that position puts them into its tile itself).  A 32-key tile
+// is [K page 0][K page 1][V page 0][V page 1]; a stage holds two tiles at head size 64 and one at 128.
+constexpr int KV_BLOCKS = D / 64;                       // column blocks of a row (streaming wants D % 64 == 0)
+constexpr int KV_PAGE_BYTES = (KV_BLOCKS ? KV_BLOCKS : 1) * 2048;  // a page's keys (or values) of one head
+constexpr int KV_TILE_BYTES = 4 * KV_PAGE_BYTES;
+constexpr bool KV_STREAMABLE = D % 64 == 0 && KV_TILE_BYTES <= ST_STAGE_BYTES;
+constexpr int KV_TILES_PER_STAGE = KV_STREAMABLE ? ST_STAGE_BYTES / KV_TILE_BYTES : 1;
+constexpr int KV_PAGES_PER_STAGE = 2 * KV_TILES_PER_STAGE;
+// byte offset of (key row r of the tile, dim c) from the tile's keys (the values lie 2 * KV_PAGE_BYTES further on)
+__device__ __forceinline__ uint32_t kv_off(int r, int c) {
+    return (uint32_t)((r >> 4) * KV_PAGE_BYTES + (c >> 6) * 2048 + (r & 15) * 128 + ((((c >> 3) & 7) ^ (r & 7)) << 4) + (c & 7) * 2);
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// S[16 x 32] = Q (fragments) * K^T for a streamed tile at shared-window address `keys`
+__device__ __forceinline__ void qk_streamed(float (&sc)[DEC_NK][4], const uint32_t (*qf)[4], const bf16* qtile16, uint32_t keys, int lane) {
+#pragma unroll
+    for (int n = 0; n < DEC_NK; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+        uint32_t a[4];
+        if (ST_Q_IN_REGS) { a[0] = qf[ks][0]; a[1] = qf[ks][1]; a[2] = qf[ks][2]; a[3] = qf[ks][3]; }
+        else load_a_frag(a, qtile16, ks, lane);
+#pragma unroll
+        for (int np = 0; np < DEC_NK / 2; ++np) {  // two n-tiles (16 keys) per ldmatrix.x4
+            uint32_t bq[4];
+            const int j = lane >> 3;
+            ldsm_x4(bq, keys + kv_off(np * 16 + (lane & 7) + (j >> 1) * 8, ks * 16 + (j & 1) * 8));
+            mma_bf16(sc[2 * np], a, bq[0], bq[1]);
+            mma_bf16(sc[2 * np + 1], a, bq[2], bq[3]);
+        }
+    }
+}
+// O[16 x D] += P (from the score accumulators, bfloat16) * V for a streamed tile whose values start at `values`
+__device__ __forceinline__ void pv_streamed(float (&o)[DTILES][4], const float (&sc)[DEC_NK][4], uint32_t values, int lane) {
+#pragma unroll
+    for (int ks = 0; ks < DEC_NK / 2; ++ks) {  // 16 keys per k-step
+        const uint32_t a[4] = {pack_bf16(sc[2 * ks][0], sc[2 * ks][1]), pack_bf16(sc[2 * ks][2], sc[2 * ks][3]),
+                               pack_bf16(sc[2 * ks + 1][0], sc[2 * ks + 1][1]), pack_bf16(sc[2 * ks + 1][2], sc[2 * ks + 1][3])};
+#pragma unroll
+        for (int dp = 0; dp < DTILES / 2; ++dp) {  // two n-tiles (16 dims) per ldmatrix.x4.trans
+            uint32_t bq[4];
+            const int j = lane >> 3;
+            ldsm_x4_trans(bq, values + kv_off(ks * 16 + (lane & 7) + (j & 1) * 8, dp * 16 + (j >> 1) * 8));
+            mma_bf16(o[2 * dp], a, bq[0], bq[1]);
+            mma_bf16(o[2 * dp + 1], a, bq[2], bq[3]);
+        }
+    }
+}
+
 // The key tiles of all requests and head groups are dealt out evenly over the blocks as in flat_attention; a block's
 // run is cut into segments at (request, head group) boundaries, a segment's tiles are packed two to a stage, and an
 // arithmetic warp takes whole stages (stage i of the segment goes to warp i mod ST_WARPS).
@@ -564,7 +614,7 @@ __device__ __forceinline__ bool stream_keys(const StackParams& p, const BlockMem
         const int lo = sg.tile0 * DEC_KT, hi = min(kvlen[sg.e], (sg.tile0 + sg.ntiles) * DEC_KT);
         const int page_lo = lo / 16, npages = (hi - lo + 15) / 16;
         const int* bt = p.meta + p.meta[META_BT_OFFSET + p.group] + (size_t)sg.e * p.meta[META_BT_STRIDE + p.group];
-        for (int pb = 0; pb < npages; pb += 32) {  // 32 pages = 16 tiles = 8 stages a round
+        for (int pb = 0; pb < npages; pb += 32) {  // 32 pages = 16 tiles a round
             int page = -1;
             if (pb + lane < npages) {
                 page = __ldg(bt + page_lo + pb + lane);
@@ -573,21 +623,21 @@ __device__ __forceinline__ bool stream_keys(const StackParams& p, const BlockMem
                     page = -1;
                 }
             }
-            for (int sb = 0; sb < 8 && pb + sb * 4 < npages; ++sb) {
-                const bool mine = (lane >> 2) == sb && page >= 0;
+            for (int sb = 0; sb < 32 / KV_PAGES_PER_STAGE && pb + sb * KV_PAGES_PER_STAGE < npages; ++sb) {
+                const bool mine = lane / KV_PAGES_PER_STAGE == sb && page >= 0;
                 const int landing = __popc(__ballot_sync(0xffffffffu, mine));
                 if (!wait_phase(b.empty + slot, free_parity, gu)) return false;
                 if (count >= (unsigned)p.inflight) {
                     if (!wait_phase(b.full + gate, gate_parity, gu)) return false;
                     if (++gate == (unsigned)p.stages) { gate = 0; gate_parity ^= 1u; }
                 }
-                if (lane == 0) mbar_expect_tx(b.full + slot, (uint32_t)landing * 2u * 2048u);
+                if (lane == 0) mbar_expect_tx(b.full + slot, (uint32_t)landing * 2u * (uint32_t)KV_PAGE_BYTES);
                 __syncwarp();
-                if (mine) {  // page q of the stage: tile q / 2, half q % 2; keys, then the values 4 KB further on
-                    const int q = lane & 3;
-                    const uint32_t dst = b.ring + slot * ST_STAGE_BYTES + (uint32_t)(q >> 1) * 8192u + (uint32_t)(q & 1) * 2048u;
-                    tma_load_2d_to(dst, cache_map, 0, ((page * 2 + 0) * p.nkv + sg.kvh) * 16, b.full + slot);
-                    tma_load_2d_to(dst + 4096u, cache_map, 0, ((page * 2 + 1) * p.nkv + sg.kvh) * 16, b.full + slot);
+                if (mine) {  // page q of the stage: tile q / 2, page q % 2 of it; keys, then the values two pages further on
+                    const int q = lane % KV_PAGES_PER_STAGE;
+                    const uint32_t dst = b.ring + slot * ST_STAGE_BYTES + (uint32_t)(q >> 1) * KV_TILE_BYTES + (uint32_t)(q & 1) * KV_PAGE_BYTES;
+                    tma_load_3d(dst, cache_map, 0, ((page * 2 + 0) * p.nkv + sg.kvh) * 16, 0, b.full + slot);
+                    tma_load_3d(dst + 2u * KV_PAGE_BYTES, cache_map, 0, ((page * 2 + 1) * p.nkv + sg.kvh) * 16, 0, b.full + slot);
                 }
                 ++count;
                 if (++slot == (unsigned)p.stages) { slot = 0; free_parity ^= 1u; }
@@ -662,8 +712,8 @@ __device__ __forceinline__ void streamed_attention(const StackParams& p, const B
                 atomicExch(&p.status[STATUS_BAD_PAGE], 1 + pos);
             }
         }
-        uint32_t qf[Q_IN_REGS ? KSTEPS : 1][4];
-        if (Q_IN_REGS) {
+        uint32_t qf[ST_Q_IN_REGS ? KSTEPS : 1][4];
+        if (ST_Q_IN_REGS) {
 #pragma unroll
             for (int ks = 0; ks < KSTEPS; ++ks) load_a_frag(qf[ks], qtile, ks, lane);
         }
@@ -671,31 +721,37 @@ __device__ __forceinline__ void streamed_attention(const StackParams& p, const B
         float o[DTILES][4];
 #pragma unroll
         for (int dt = 0; dt < DTILES; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
-        const int nstages = (sg.ntiles + 1) / 2;
-        for (int si = warp; si < nstages; si += ST_WARPS) {
+        const int nstages = (sg.ntiles + KV_TILES_PER_STAGE - 1) / KV_TILES_PER_STAGE;
+        // Which warp takes a stage is a matter of the ring slot it lies in (slot mod warps; the ring has a multiple of
+        // ST_WARPS slots when keys are streamed): a warp then only ever waits for slots whose earlier contents it has
+        // used itself.  A warp that waited for a slot another warp empties could find the slot's barrier a phase
+        // behind (that stage still on its way) and, parities being one bit, take it for the phase it wants.
+        const int first_si = (int)(((unsigned)warp + (unsigned)ST_WARPS - (cur.slot + stage0) % (unsigned)ST_WARPS) % (unsigned)ST_WARPS);
+        for (int si = first_si; si < nstages; si += ST_WARPS) {
             const unsigned n = cur.slot + stage0 + (unsigned)si, slot = n % (unsigned)p.stages;
             wait_phase(b.full + slot, cur.parity ^ ((n / (unsigned)p.stages) & 1u), gu);
             unsigned char* st = b.ring_ptr + (size_t)slot * ST_STAGE_BYTES;
+            const uint32_t st_addr = b.ring + slot * ST_STAGE_BYTES;
             bool wrote = false;
-            for (int j = 0; j < 2 && si * 2 + j < sg.ntiles; ++j) {
-                bf16* ktile = reinterpret_cast<bf16*>(st + j * 8192);
-                bf16* vtile = ktile + DEC_KT * LDS;
-                const int k0 = lo + (si * 2 + j) * DEC_KT;
+            for (int j = 0; j < KV_TILES_PER_STAGE && si * KV_TILES_PER_STAGE + j < sg.ntiles; ++j) {
+                unsigned char* keys = st + j * KV_TILE_BYTES;
+                unsigned char* values = keys + 2 * KV_PAGE_BYTES;
+                const int k0 = lo + (si * KV_TILES_PER_STAGE + j) * DEC_KT;
                 if (owner && pos >= k0 && pos < k0 + DEC_KT) {  // the tile with the newest position
                     const int r = pos - k0;  // its row; the rows after it hold nothing: their values must be zeros
                     for (int i = lane; i < D; i += 32) {
-                        ktile[toff(r, i)] = newest[i];
-                        vtile[toff(r, i)] = newest[D + i];
+                        *reinterpret_cast<bf16*>(keys + kv_off(r, i)) = newest[i];
+                        *reinterpret_cast<bf16*>(values + kv_off(r, i)) = newest[D + i];
                     }
                     for (int idx = lane; idx < (DEC_KT - 1 - r) * (D / 8); idx += 32) {
                         const int rr = r + 1 + idx / (D / 8), c8 = (idx % (D / 8)) * 8;
-                        *reinterpret_cast<uint4*>(vtile + toff(rr, c8)) = make_uint4(0u, 0u, 0u, 0u);
+                        *reinterpret_cast<uint4*>(values + kv_off(rr, c8)) = make_uint4(0u, 0u, 0u, 0u);
                     }
                     wrote = true;
                     __syncwarp();
                 }
                 float sc[DEC_NK][4];
-                qk_tile<DEC_NK>(sc, qf, qtile, ktile, lane);
+                qk_streamed(sc, qf, qtile, st_addr + j * KV_TILE_BYTES, lane);
 #pragma unroll
                 for (int nn = 0; nn < DEC_NK; ++nn)
 #pragma unroll
@@ -704,7 +760,7 @@ __device__ __forceinline__ void streamed_attention(const StackParams& p, const B
                         sc[nn][c] = key < hi ? sc[nn][c] * p.scale_log2 : -INFINITY;
                     }
                 softmax_tile<DEC_NK>(sc, m, l, o);
-                pv_tile<DEC_NK>(o, sc, vtile, lane);
+                pv_streamed(o, sc, st_addr + j * KV_TILE_BYTES + 2 * KV_PAGE_BYTES, lane);
             }
             __syncwarp();
             if (wrote) fence_async();  // the copy engine writes this stage next
@@ -940,16 +996,17 @@ bool make_map(CUtensorMap* map, const void* base, long long rows, long long K, i
     return true;
 }
 
-// A layer's pages [pages, 2, nkv, 16, 64] as rows of 64: one box is a page's keys (or values) of one head.
+// A layer's pages [pages, 2, nkv, 16, D] as rows of D in 64-wide column blocks: one box is a page's keys (or values) of
+// one head, landing as D / 64 blocks of [16][64].
 bool make_cache_map(CUtensorMap* map, const void* base, long long rows) {
     EncodeTiledFn fn = encode_fn();
-    if (!fn || rows <= 0 || ((uintptr_t)base & 15)) return false;
+    if (!fn || rows <= 0 || ((uintptr_t)base & 15) || D % 64) return false;
     alignas(64) CUtensorMap tmp;
-    cuuint64_t dims[2] = {64, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {128};
-    cuuint32_t box[2] = {64, 16};
-    cuuint32_t estr[2] = {1, 1};
-    if (fn(&tmp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+    cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(D / 64)};
+    cuuint64_t strides[2] = {(cuuint64_t)D * 2, 128};
+    cuuint32_t box[3] = {64, 16, (cuuint32_t)(D / 64)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    if (fn(&tmp, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return false;
@@ -976,6 +1033,7 @@ StackPlan stack_plan(int M, int xwidth) {
     if (fixed + (size_t)ST_MIN_STAGES * ST_STAGE_BYTES > (size_t)smem_max) return plan;
     int stages = (int)(((size_t)smem_max - fixed) / ST_STAGE_BYTES);
     if (stages > ST_MAX_STAGES) stages = ST_MAX_STAGES;
+    if (stages >= ST_WARPS) stages -= stages % ST_WARPS;  // whole rounds of the warps (see streamed_attention); fewer: keys are not streamed
     const size_t smem = fixed + (size_t)stages * ST_STAGE_BYTES;
     static size_t configured[64] = {};
     if (dev < 0 || dev >= 64) return plan;
@@ -1010,14 +1068,14 @@ extern "C" int decode_stack_fill_layer(void* dst, const void* w_qkv, const void*
     if (!make_map(&ly.map_qkv, w_qkv, (long long)(nq + 2 * nkv) * D, H, 16, ST_KC / 64) || !make_map(&ly.map_o, w_o, H, (long long)nq * D, 16, ST_KC / 64) ||
         !make_map(&ly.map_gate_up, w_gate_up, 2ll * I, H, 8, ST_KC / 64) || !make_map(&ly.map_down, w_down, H, I, 16, ST_KC / 64))
         return (int)cudaErrorInvalidValue;
-    if (D == 64 && page_size == 16 && !make_cache_map(&ly.map_cache, cache, (long long)num_pages * 2 * nkv * 16)) return (int)cudaErrorInvalidValue;
+    if (KV_STREAMABLE && page_size == 16 && !make_cache_map(&ly.map_cache, cache, (long long)num_pages * 2 * nkv * 16)) return (int)cudaErrorInvalidValue;
     ly.norm1 = norm1; ly.norm2 = norm2; ly.inv_freq = inv_freq; ly.cache = (bf16*)cache; ly.store_kv = store_kv;
     memcpy(dst, &ly, sizeof(ly));
     return 0;
 }
 
 // For tests and measurements: 0 = the attention fetches keys and values itself (the only way with a window, a head
-// size other than 64 or pages other than 16), 1 (the default) = the stream warp brings them where it can.
+// size other than 64 or 128, or pages other than 16), 1 (the default) = the stream warp brings them where it can.
 extern "C" void decode_stack_set_stream_kv(int on) { g_stack_stream_kv = on; }
 
 // For measurements: the most parts a (request, head group) pair is cut into (one part a pair at batch 8, 64 blocks
@@ -1090,7 +1148,7 @@ extern "C" int decode_stack(const void* layers, int num_layers, void* resid, con
     p.eps = eps; p.scale_log2 = scale * LOG2E;
     p.times = g_stack_times;
     p.max_split = g_stack_max_split;
-    p.stream_kv = (g_stack_stream_kv && all_store_kv && D == 64 && page_size == 16 && window == 0) ? 1 : 0;
+    p.stream_kv = (g_stack_stream_kv && all_store_kv && KV_STREAMABLE && page_size == 16 && window == 0 && plan.stages % ST_WARPS == 0) ? 1 : 0;
     p.inflight = g_stack_inflight > 0 ? g_stack_inflight : ST_INFLIGHT;
     if (p.inflight > p.stages) p.inflight = p.stages;
     const int region_bytes = (int)stack_region_bytes(M, xwidth);

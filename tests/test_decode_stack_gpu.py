@@ -60,7 +60,8 @@ def _decode_and_compare(lm, cfg, w, lengths, steps, seed, one_launch=True):
     ("B", 16, [5, 64, 65, 127, 128, 129, 300, 2, 47, 48, 49]),  # 11 rows: two n-tiles
     ("B", 16, [30 + 7 * i for i in range(16)]),             # 16 rows
     ("B", 8, [1, 7, 8, 9, 33, 150]),                        # pages of 8: the attention fetches keys and values itself
-    ("C", 16, [3, 16, 100, 130, 17]),                       # head size 128: four arithmetic warps
+    ("C", 16, [3, 16, 100, 130, 17]),                       # head size 128: four arithmetic warps, one tile a stage
+    ("C", 16, [20 + 9 * i for i in range(16)]),             # head size 128, two n-tiles
 ])
 def test_layer_kernel_against_plain_and_parts(tiny_models, name, page, lengths):
     d, cfg, _ = tiny_models[name]
