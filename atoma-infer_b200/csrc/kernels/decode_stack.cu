@@ -5,19 +5,25 @@
 // stops at every kernel boundary: a linear of a few microseconds spends a third of its time starting and
 // draining, and the norms and the attention between the linears read no weights at all.  Here one block per
 // multiprocessor stays resident for all layers, and a warp of its own does nothing but stream the block's share
-// of every weight matrix, in the order the layers use them, through a ring of shared-memory stages (bulk async
-// copies that complete on mbarriers).  The stream depends on nothing the step computes, so it runs ahead of
-// the arithmetic by the depth of the ring: while the blocks wait for each other between two phases, compute a
-// norm, or walk keys and values, the next linears' weights keep arriving.
+// of every weight matrix, in the order the layers use them, through a ring of 16 KB shared-memory stages: one
+// tensor-map box a stage (`cp.async.bulk.tensor`, completion on an mbarrier), the matrix seen in 64-wide column
+// groups so that a box lands as 128-byte-swizzled [rows][64] blocks that ldmatrix reads without bank conflicts.
+// The stream depends on nothing the step computes, so it runs ahead of the arithmetic by the depth of the ring:
+// while the blocks wait for each other between two phases or merge attention results, the next linears' weights
+// keep arriving.  With pages of 16 keys and head size 64 or 128 the same warp streams the layer's keys and values.
 //
 // A layer is five phases with a grid-wide barrier after each (the layer of models/src/llama.rs:393-410):
-//   1. RMSNorm of the residual rows (every block computes it for itself, into shared memory), then the fused
-//      q/k/v projection;
-//   2. rotation of q and k, the new key and value written to their page, attention over the cached pages (the
-//      key tiles of all requests dealt out evenly over the blocks, flat_attention in attention_tiles.cuh);
+//   1. the rows of x for the q/k/v projection by TMA into shared memory, and the projection;
+//   2. rotation of q and k, the new key and value written to their page, attention over the cached pages: the
+//      (request, head group) pairs dealt to the blocks, cut into blocks / pairs parts each;
 //   3. output projection, added into the float32 residual;
-//   4. RMSNorm again, gate/up projection with the SwiGLU epilogue;
-//   5. down projection, added into the residual.
+//   4. the rows of x again, gate/up projection with the SwiGLU epilogue;
+//   5. down projection (x in 512-wide chunks through a second, small ring), added into the residual.
+// RMSNorm has no phase of its own: the epilogue of a phase that adds into the residual (3 and 5) also writes the new
+// residual times the following norm's weight in bfloat16 (the next linear's x) and, per tile and row, the sum of
+// squares; the next linear adds those up in a fixed order and scales its products' rows by 1 / rms, which commutes
+// with the product.  (Every block computing the norm for itself, from the float32 rows, cost 8 to 9 us a norm: 148
+// blocks reading the same fresh lines from L2, half of them across the two dies.)
 // A linear's 16-row weight tiles (16 output columns) are dealt to the blocks like cards, the deal going on from
 // phase to phase, so over a layer every block streams the same number of bytes, give or take a tile; a block
 // multiplies a whole tile (all of K) itself: its arithmetic warps split each 512-wide stage between them
