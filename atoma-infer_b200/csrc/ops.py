@@ -24,7 +24,7 @@ MAX_GROUPS = 8
 STATUS_WORDS = 8
 SKINNY_MAX_ROWS = 16  # bfloat16 linears with at most this many rows stream the weights
 
-CORE_SOURCES = ["kernels/core.cu", "kernels/linear_bf16.cu", "kernels/sampling.cu"]
+CORE_SOURCES = ["kernels/core.cu", "kernels/linear_bf16.cu", "kernels/linear_stream.cu", "kernels/sampling.cu"]
 ATTENTION_SOURCES = ["kernels/attention_bf16.cu"]
 GEMM_SOURCES = ["kernels/gemm_tcgen05.cu"]
 ATTENTION_TC_SOURCES = ["kernels/attention_tcgen05.cu"]
@@ -86,6 +86,10 @@ class CudaOps:
         mode = os.environ.get("ATOMA_INFER_PDL", "linear+norm")
         self.pdl = {"0": 0, "1": 1, "linear": 2, "linear+norm": 6}.get(mode, 6)
         self.fused_rope = True  # the decode attention rotates q and k and writes the new key and value itself
+        # Few-row linears go to the persistent, TMA-fed kernel (kernels/linear_stream.cu) where it is the faster one
+        # (see _stream_linear); ATOMA_INFER_STREAM_LINEAR=0 keeps them all on the kernel that loads weights into
+        # fragments directly (kernels/linear_bf16.cu).  The kernel tests set the attribute.
+        self.stream_linear = os.environ.get("ATOMA_INFER_STREAM_LINEAR", "1") != "0"
         # Decode steps of at most 16 rows can run stretches of whole layers as one persistent kernel (ATOMA_INFER_FUSED_LAYERS=1;
         # off by default while it is slower than the step part by part)
         self.fused_layers = os.environ.get("ATOMA_INFER_FUSED_LAYERS", "0") == "1"
@@ -123,6 +127,7 @@ class CudaOps:
                 f"a tensor-core GEMM block ({s[2] - 1}) gave up waiting on a barrier" if s[2] else
                 f"a tensor-core attention block ({s[3] - 1}) gave up waiting on a barrier" if s[3] else
                 f"a block ({s[4] - 1}) of the decode step's layer kernel gave up waiting" if s[4] else
+                f"a block ({s[5] - 1}) of the streamed few-row linear gave up waiting" if s[5] else
                 f"status words {s}")
 
     def clear_status(self) -> None:
@@ -201,6 +206,12 @@ class CudaOps:
                 self.silu_mul(y, out, meta, M, n_out)
                 return out
             return y
+        if self._stream_linear(M, N, K) and x.is_contiguous() and w.is_contiguous():
+            y = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
+            self._note_weight(w)
+            self._check(self.lib.linear_stream(_p(x), _p(w), _p(y), _code(y), int(silu_mul), M, N, K, _p(self.status),
+                                               self._stream()), "linear_stream")
+            return y
         if M <= SKINNY_MAX_ROWS and K % 8 == 0:
             y = torch.empty((M, n_out), dtype=out_dtype, device=x.device)
             self._note_weight(w)
@@ -218,6 +229,18 @@ class CudaOps:
             self.silu_mul(y, out, meta, M, n_out)
             return out
         return y
+
+    def _stream_linear(self, M: int, N: int, K: int) -> bool:
+        """Whether a bfloat16 linear of M <= 16 rows runs on the TMA-fed persistent kernel.  Measured, decode step as a
+        CUDA graph, direct against streamed: Llama 3.2 1B sizes, batch 1 / 2 / 4 / 8 / 12 / 16: 0.758 / 0.800 / 0.831 /
+        0.878 / 1.125 / 1.265 ms against 0.778 / 0.791 / 0.805 / 0.829 / 0.918 / 0.944; 8 layers of the 3B sizes, batch
+        1 / 8: 0.539 / 0.656 against 0.559 / 0.646; of the 8B sizes: 0.918 / 1.040 against 0.814 / 0.912.  So: two rows
+        and more always (the direct kernel is a quarter to a third slower with two n-tiles, 9 to 16 rows); a single row
+        only where every matrix is large (both sides at least 4,096), since a persistent kernel holds the whole GPU and
+        the kernel after it cannot start early.  Mixing the two within a layer was the slowest choice at batch 1."""
+        if not self.stream_linear or M > SKINNY_MAX_ROWS or K % 64:
+            return False
+        return M >= 2 or min(N, K) >= 4096
 
     def _swiglu_on_tcgen05(self, M: int, n_out: int, K: int) -> bool:
         """Whether the gate/up product with the SwiGLU epilogue runs on the persistent tcgen05 kernel instead

@@ -146,6 +146,50 @@ def test_few_row_linear_with_every_split_of_k(rts, M, N, Kd):
         rt.ops.lib.linear_skinny_set_ksplit(0)
 
 
+@pytest.mark.parametrize("M,N,Kd,silu,out", [
+    (1, 4100, 4096, False, "bfloat16"),    # one row: a matrix with both sides at least 4,096 streams
+    (2, 272, 2048, False, "bfloat16"),     # few tiles: most blocks stay out
+    (7, 1000, 192, False, "float32"),      # K no multiple of 512 (a stage that is part zeros), N no multiple of 16
+    (8, 3072, 2048, False, "bfloat16"),
+    (9, 40, 64, False, "float32"),         # two n-tiles, one group of k
+    (16, 2048, 8192, False, "bfloat16"),   # x too large to stay in shared memory: in chunks through its own ring
+    (13, 2 * 520, 1088, True, "bfloat16"), # silu(gate) * up, columns no multiple of 8, x in chunks (13 rows of 1,088 stay; 17 chunks)
+    (16, 2 * 8192, 2048, True, "bfloat16"),
+    (5, 2 * 176, 4160, True, "bfloat16"),
+])
+def test_streamed_few_row_linear(rts, M, N, Kd, silu, out):
+    """The TMA-fed persistent linear (kernels/linear_stream.cu) against the product in float64, for shapes that meet
+    every branch: rows of x resident or in chunks, one and two n-tiles, partial last stage, partial last tile, both
+    epilogues and both output types; the same call twice gives the same bits; the direct kernel gives the same
+    product within rounding."""
+    rt = rts["bfloat16"]
+    ops = rt.ops
+    g = torch.Generator().manual_seed(N + M)
+    x = torch.randn(M, Kd, generator=g).bfloat16()
+    w = (torch.randn(N, Kd, generator=g) / math.sqrt(Kd)).bfloat16()
+    full = x.double() @ w.double().T
+    want = full[:, :N // 2] * torch.sigmoid(full[:, :N // 2]) * full[:, N // 2:] if silu else full
+    xd, wd = x.to(rt.device), w.to(rt.device)
+    odt = torch.float32 if out == "float32" else torch.bfloat16
+    was = ops.stream_linear
+    try:
+        ops.stream_linear = True
+        assert ops._stream_linear(M, N, Kd), "the shape was meant to take the streamed kernel"
+        before = ops.launches
+        y = ops.linear(xd, wd, out_dtype=odt, silu_mul=silu)
+        assert ops.launches == before + 1
+        ops.check_status()
+        tol = (2e-3 if out == "float32" else 2e-2) * want.abs().max()
+        assert y.shape == want.shape and y.dtype == odt
+        assert (y.double().cpu() - want).abs().max() < tol
+        assert torch.equal(y, ops.linear(xd, wd, out_dtype=odt, silu_mul=silu))
+        ops.stream_linear = False
+        z = ops.linear(xd, wd, out_dtype=odt, silu_mul=silu)
+        assert (z.double().cpu() - want).abs().max() < tol
+    finally:
+        ops.stream_linear = was
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("M", [2, 8, 13, 33])
 def test_swiglu_gate_epilogue(rts, dtype, M):
