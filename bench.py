@@ -157,6 +157,68 @@ def serving_workload(which: str) -> int:
     return 0
 
 
+def few_row_linears(which: str) -> int:
+    """Times the two few-row linear kernels on the four matrices of a layer: 32 calls in one CUDA graph that cycle
+    through as many weight sets as fit 2.5 GB (so no weight is found in L2), CUDA events around three replays."""
+    import torch
+
+    import atoma_infer_b200  # noqa: F401
+    from atoma_infer_b200.engine.runtime import make_runtime
+
+    H, I, nq, nkv, d = {"1b": (2048, 8192, 32, 8, 64), "3b": (3072, 8192, 24, 8, 128), "8b": (4096, 14336, 32, 8, 128)}[which]
+    shapes = {"q/k/v": ((nq + 2 * nkv) * d, H, False), "output": (H, nq * d, False), "gate/up + SwiGLU": (2 * I, H, True),
+              "down": (H, I, False)}
+    rt = make_runtime("bfloat16", "cuda:0")
+    ops, dev = rt.ops, rt.device
+    hbm = peaks()[0]
+
+    def graph_us(fn, n=32):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(n):
+                fn()
+        g.replay()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        for _ in range(3):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / (3 * n) * 1e3
+
+    print(f"few-row linears, Llama sizes {which}: us a call, direct | streamed (at the copy bandwidth {hbm:.0f} GB/s: ideal)")
+    for name, (N, K, silu) in shapes.items():
+        sets = max(2, min(16, int(2.5e9 // (N * K * 2))))
+        ws = [torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(sets)]
+        row = []
+        for M in (1, 8, 16):
+            x = torch.randn(M, K, device=dev, dtype=torch.bfloat16)
+            cell = []
+            for streamed in (False, True):
+                ops.stream_linear = streamed
+                if streamed and not ops._stream_linear(2, N, K):
+                    cell.append(float("nan"))
+                    continue
+                calls = [0]
+
+                def call():
+                    if streamed:  # whatever the policy for this row count says
+                        ops.linear_streamed(x, ws[calls[0] % sets], silu_mul=silu)
+                    else:
+                        ops.linear(x, ws[calls[0] % sets], silu_mul=silu)
+                    calls[0] += 1
+                cell.append(graph_us(call))
+            row.append(f"{M:2d} rows {cell[0]:6.1f} | {cell[1]:6.1f}")
+        print(f"  {name:18s} {N:6d} x {K:5d} ({N * K * 2 / 1e6:6.1f} MB, ideal {N * K * 2 / hbm / 1e3:5.1f}):  " + "   ".join(row))
+        del ws
+    ops.check_status()
+    return 0
+
+
 def layer_kernel_phases(eng, args, prompt, greedy, cfg) -> int:
     """Decode steps through the persistent layer kernel (csrc/kernels/decode_stack.cu), eagerly, with every block
     writing the global clock after each phase and each barrier of each layer; prints the mean, the slowest and the
@@ -258,6 +320,9 @@ def main() -> int:
     ap.add_argument("--layer-kernel-phases", action="store_true",
                     help="instead of the benchmark: decode steps with the persistent layer kernel switched on, and the "
                          "time its blocks spend in every phase and at every barrier of a layer (a table, for profiles/)")
+    ap.add_argument("--linears", action="store_true",
+                    help="instead of the benchmark: the four linears of a layer (sizes of --model) at 1, 8 and 16 rows on the "
+                         "direct and on the streamed few-row kernel, weights cold (a table, for profiles/)")
     ap.add_argument("--phase", default="all", choices=["all", "prefill", "decode"],
                     help="measure only one phase (for profiling); the JSON line then lacks the other")
     args = ap.parse_args()
@@ -272,6 +337,8 @@ def main() -> int:
             print(f"bench.py measures a one-GPU engine; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.linears:
+        return few_row_linears(args.model)
     if args.model != "1b":
         return serving_workload(args.model)
 
