@@ -106,12 +106,27 @@ __device__ __forceinline__ bool ls_wait(uint64_t* bar, uint32_t parity, const Ls
     return false;
 }
 
+// An RMSNorm folded into the linears around it (optional).  The linear BEFORE the norm (EPI 2) adds its product into the
+// float32 residual stream and leaves, for the norm: the new residual times the norm's weight in bfloat16 (the next
+// linear's x), and per 16-column tile and row the sum of squares of the new residual.  The linear AFTER the norm gets
+// those sums (`ss_in`, `ss_parts` tiles of 16 floats), adds them up in tile order, and scales its products' rows by
+// 1 / sqrt(sum / width + eps): a factor per row commutes with the product.
+struct LsNorm {
+    const float* ss_in;    // [ss_parts][16] sums of squares left by the linear before (null: x is used as it is)
+    int ss_parts, width;   // width: the norm's (the residual's) width
+    float eps;
+    float* resid;          // EPI 2: [M, N] float32, updated in place
+    const float* next_w;   // EPI 2: weight of the norm that follows (null: nothing follows, only the residual is updated)
+    bf16* xw_out;          // EPI 2: [M, N] residual * next_w
+    float* ss_out;         // EPI 2: [tiles][16]
+};
+
 // NT: n-tiles of 8 rows of x.  XMODE 0: all rows of x lie in shared memory; 1: x comes in chunks through a ring.
-// EPI 1: w is [gate; up] stacked, the result silu(gate) * up of N / 2 columns.
+// EPI 1: w is [gate; up] stacked, the result silu(gate) * up of N / 2 columns.  EPI 2: added into the residual (LsNorm).
 template <int NT, int XMODE, int EPI, typename TO>
 __global__ void __launch_bounds__(LS_THREADS, 1)
 linear_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap, TO* __restrict__ y, int M,
-                     int N, int K, int stages, int inflight, int* __restrict__ status) {
+                     int N, int K, int stages, int inflight, const LsNorm norm, int* __restrict__ status) {
     constexpr int ROWS = NT * 8;
     constexpr int RED_STRIDE = ROWS + 1;
     constexpr int RED_FLOATS = LS_WARPS * 16 * RED_STRIDE;
@@ -132,6 +147,7 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_cons
     uint64_t* xempty = xfull + LS_XRING;
     uint64_t* xbar = xempty + LS_XRING;
     volatile int* gave_up = reinterpret_cast<volatile int*>(xbar + 1);
+    float* inv = reinterpret_cast<float*>(const_cast<int*>(gave_up) + 2);  // [16] 1 / rms of the rows (norm.ss_in)
     const LsGiveup gu{gave_up, status, 1 + (int)blockIdx.x};
     const int n_out = EPI == 1 ? N / 2 : N, out_rows = EPI == 1 ? 8 : 16;
     const int tiles = EPI == 1 ? (n_out + 7) / 8 : (N + 15) / 16;
@@ -211,6 +227,17 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_cons
                 for (unsigned f = 0; f < ahead && f < xtotal; ++f) x_issue();
             }
         }
+        if (norm.ss_in) {  // the rows' scales, from the sums of squares the linear before left (in tile order)
+            for (int m = warp; m < LS_MAX_ROWS; m += LS_WARPS) {
+                float ss = 0.f;
+                if (m < M)
+                    for (int i = lane; i < norm.ss_parts; i += 32) ss += __ldcg(norm.ss_in + (size_t)i * LS_MAX_ROWS + m);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (lane == 0) inv[m] = m < M ? rsqrtf(ss / (float)norm.width + norm.eps) : 0.f;
+            }
+            ls_consumer_sync();
+        }
         if (XMODE == 0 && mine > 0) {
             // beyond the last group of the rows a stage holds zeros, but the region holds whatever was there, and zero
             // times NaN is NaN: the rest of the last chunk is zeroed
@@ -288,18 +315,39 @@ linear_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_cons
                 r1[0] = acc[0][t][2]; r1[1] = acc[0][t][3];
             }
             ls_consumer_sync();
-            for (int idx = tid; idx < out_rows * ROWS; idx += LS_CONSUMERS) {
+            for (int idx = tid; idx < out_rows * ROWS; idx += LS_CONSUMERS) {  // whole warps take part or stay out
                 const int m = idx / out_rows, r = idx % out_rows;  // consecutive threads, consecutive columns
                 const int col = tile * out_rows + r;
-                if (m >= M || col >= n_out) continue;
+                const bool on = m < M && col < n_out;
                 float v = 0.f, u = 0.f;
 #pragma unroll
                 for (int wi = 0; wi < LS_WARPS; ++wi) {
                     v += red[(wi * 16 + r) * RED_STRIDE + m];
                     if (EPI == 1) u += red[(wi * 16 + r + 8) * RED_STRIDE + m];
                 }
-                if (EPI == 1) v = v / (1.f + expf(-v)) * u;
-                y[(size_t)m * n_out + col] = from_float<TO>(v);
+                if (EPI == 2) {
+                    // into the residual; for the norm after it: the new value times the norm's weight, and the tile's
+                    // share of the row's sum of squares (the 16 lanes that hold a row's 16 columns add up)
+                    float now = 0.f;
+                    if (on) {
+                        float* dst = norm.resid + (size_t)m * n_out + col;
+                        now = *dst + v;
+                        *dst = now;
+                        if (norm.next_w) norm.xw_out[(size_t)m * n_out + col] = __float2bfloat16_rn(now * norm.next_w[col]);
+                    }
+                    if (norm.next_w) {
+                        float sq = now * now;
+                        sq += __shfl_xor_sync(0xffffffffu, sq, 8);
+                        sq += __shfl_xor_sync(0xffffffffu, sq, 4);
+                        sq += __shfl_xor_sync(0xffffffffu, sq, 2);
+                        sq += __shfl_xor_sync(0xffffffffu, sq, 1);
+                        if (r == 0) norm.ss_out[(size_t)tile * LS_MAX_ROWS + m] = m < M ? sq : 0.f;
+                    }
+                } else if (on) {
+                    if (norm.ss_in) { v *= inv[m]; u *= inv[m]; }
+                    if (EPI == 1) v = v / (1.f + expf(-v)) * u;
+                    y[(size_t)m * n_out + col] = from_float<TO>(v);
+                }
             }
             ++done;  // the other reduction buffer next: this one may still be read
         }
@@ -341,7 +389,7 @@ struct LsPlan { int blocks, stages, xmode; size_t smem; };
 
 template <int NT, int XMODE, int EPI, typename TO>
 int ls_launch(const CUtensorMap& wmap, const CUtensorMap& xmap, void* y, int M, int N, int K, const LsPlan& plan, int tiles,
-              int* status, cudaStream_t stream) {
+              const LsNorm& norm, int* status, cudaStream_t stream) {
     auto kernel = linear_stream_kernel<NT, XMODE, EPI, TO>;
     static size_t configured[64] = {};
     int dev = 0;
@@ -362,7 +410,7 @@ int ls_launch(const CUtensorMap& wmap, const CUtensorMap& xmap, void* y, int M, 
     cfg.attrs = attr;
     cfg.numAttrs = (g_use_pdl & 3) ? 1 : 0;
     int inflight = plan.stages < 6 ? plan.stages : 6;
-    cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, wmap, xmap, (TO*)y, M, N, K, plan.stages, inflight, status);
+    cudaError_t err = cudaLaunchKernelEx(&cfg, kernel, wmap, xmap, (TO*)y, M, N, K, plan.stages, inflight, norm, status);
     if (err != cudaSuccess) return (int)err;
     LAUNCH_RETURN();
 }
@@ -378,10 +426,20 @@ extern "C" int linear_stream_supports(int M, int N, int K, int epilogue) {
 
 // x [M, K] and w [N, K] bfloat16, both 16-byte aligned; y [M, N] (epilogue 1: [M, N / 2] = silu(gate) * up for w =
 // [gate; up]) bfloat16 or float32 (out_dtype).  status: the device status words (may be null).
-extern "C" int linear_stream(const void* x, const void* w, void* y, int out_dtype, int epilogue, int M, int N, int K, int* status,
-                             cudaStream_t stream) {
+// A norm folded in (see LsNorm), all optional: ss_in ([ss_parts][16] floats, with norm_width and eps): the rows of the
+// result are scaled by the rows' 1 / rms.  epilogue 2: nothing is written to y; the product is added into resid [M, N]
+// (float32) and, if next_w is given, xw_out [M, N] (bfloat16) and ss_out [ceil(N / 16)][16] are left for the linear after
+// the next norm.
+extern "C" int linear_stream_norm(const void* x, const void* w, void* y, int out_dtype, int epilogue, int M, int N, int K,
+                                  const float* ss_in, int ss_parts, int norm_width, float eps, float* resid, const float* next_w,
+                                  void* xw_out, float* ss_out, int* status, cudaStream_t stream) {
     if (!linear_stream_supports(M, N, K, epilogue)) return (int)cudaErrorInvalidValue;
     if (epilogue == 1 && out_dtype != DT_BF16) return (int)cudaErrorInvalidValue;
+    if (epilogue == 2 && (!resid || (next_w && (!xw_out || !ss_out)))) return (int)cudaErrorInvalidValue;
+    if (ss_in && (ss_parts <= 0 || norm_width <= 0)) return (int)cudaErrorInvalidValue;
+    LsNorm norm;
+    norm.ss_in = ss_in; norm.ss_parts = ss_parts; norm.width = norm_width; norm.eps = eps;
+    norm.resid = resid; norm.next_w = next_w; norm.xw_out = (bf16*)xw_out; norm.ss_out = ss_out;
     int dev = 0, sms = 0, smem_max = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return (int)cudaErrorInvalidDevice;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return (int)cudaErrorInvalidDevice;
@@ -392,7 +450,7 @@ extern "C" int linear_stream(const void* x, const void* w, void* y, int out_dtyp
     plan.xmode = x_all <= LS_X_RESIDENT ? 0 : 1;
     const size_t region = plan.xmode == 0 ? x_all : (size_t)LS_XRING * rows * 1024;
     const size_t red = (size_t)(2 * LS_WARPS * 16 * (rows + 1) + 1) * sizeof(float);
-    const size_t fixed = region + red + (2 * LS_MAX_STAGES + 2 * LS_XRING + 1) * sizeof(uint64_t) + 64 + 1024;
+    const size_t fixed = region + red + (2 * LS_MAX_STAGES + 2 * LS_XRING + 1) * sizeof(uint64_t) + 64 + LS_MAX_ROWS * sizeof(float) + 1024;
     if (fixed + (size_t)LS_MIN_STAGES * LS_STAGE_BYTES > (size_t)smem_max) return (int)cudaErrorInvalidConfiguration;
     plan.stages = (int)(((size_t)smem_max - fixed) / LS_STAGE_BYTES);
     if (plan.stages > LS_MAX_STAGES) plan.stages = LS_MAX_STAGES;
@@ -405,9 +463,10 @@ extern "C" int linear_stream(const void* x, const void* w, void* y, int out_dtyp
     const int xgroups = plan.xmode == 0 ? K / 64 : LS_KC / 64;
     if (xgroups > 256 || !ls_make_map(&xmap, x, M, K, rows, xgroups)) return (int)cudaErrorInvalidValue;
 #define LS_CASE(NT, XM) \
-    if (epilogue == 1) return ls_launch<NT, XM, 1, __nv_bfloat16>(wmap, xmap, y, M, N, K, plan, tiles, status, stream); \
-    if (out_dtype == DT_F32) return ls_launch<NT, XM, 0, float>(wmap, xmap, y, M, N, K, plan, tiles, status, stream); \
-    return ls_launch<NT, XM, 0, __nv_bfloat16>(wmap, xmap, y, M, N, K, plan, tiles, status, stream)
+    if (epilogue == 2) return ls_launch<NT, XM, 2, float>(wmap, xmap, y, M, N, K, plan, tiles, norm, status, stream); \
+    if (epilogue == 1) return ls_launch<NT, XM, 1, __nv_bfloat16>(wmap, xmap, y, M, N, K, plan, tiles, norm, status, stream); \
+    if (out_dtype == DT_F32) return ls_launch<NT, XM, 0, float>(wmap, xmap, y, M, N, K, plan, tiles, norm, status, stream); \
+    return ls_launch<NT, XM, 0, __nv_bfloat16>(wmap, xmap, y, M, N, K, plan, tiles, norm, status, stream)
     if (rows == 8) {
         if (plan.xmode == 0) { LS_CASE(1, 0); }
         LS_CASE(1, 1);
@@ -415,4 +474,12 @@ extern "C" int linear_stream(const void* x, const void* w, void* y, int out_dtyp
     if (plan.xmode == 0) { LS_CASE(2, 0); }
     LS_CASE(2, 1);
 #undef LS_CASE
+}
+
+// The plain product (no norm folded in).
+extern "C" int linear_stream(const void* x, const void* w, void* y, int out_dtype, int epilogue, int M, int N, int K, int* status,
+                             cudaStream_t stream) {
+    if (epilogue == 2) return (int)cudaErrorInvalidValue;
+    return linear_stream_norm(x, w, y, out_dtype, epilogue, M, N, K, nullptr, 0, 0, 0.f, nullptr, nullptr, nullptr, nullptr, status,
+                              stream);
 }

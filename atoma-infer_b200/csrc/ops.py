@@ -90,6 +90,9 @@ class CudaOps:
         # (see _stream_linear); ATOMA_INFER_STREAM_LINEAR=0 keeps them all on the kernel that loads weights into
         # fragments directly (kernels/linear_bf16.cu).  The kernel tests set the attribute.
         self.stream_linear = os.environ.get("ATOMA_INFER_STREAM_LINEAR", "1") != "0"
+        # In decode steps whose linears are streamed, the RMSNorms between them are folded into them (parts/decode_stack.py,
+        # the chain); ATOMA_INFER_FOLD_NORMS=0 leaves the norm a kernel of its own.
+        self.fold_norms = os.environ.get("ATOMA_INFER_FOLD_NORMS", "1") != "0"
         # Decode steps of at most 16 rows can run stretches of whole layers as one persistent kernel (ATOMA_INFER_FUSED_LAYERS=1;
         # off by default while it is slower than the step part by part)
         self.fused_layers = os.environ.get("ATOMA_INFER_FUSED_LAYERS", "0") == "1"
@@ -226,15 +229,30 @@ class CudaOps:
             return out
         return y
 
-    def linear_streamed(self, x, w, *, out_dtype=None, silu_mul: bool = False):
+    def linear_streamed(self, x, w, *, out_dtype=None, silu_mul: bool = False, scale_from=None, add_into=None):
         """``linear`` on the TMA-fed persistent kernel whatever the policy says (bfloat16, at most 16 rows, K a multiple
-        of 64, contiguous operands)."""
+        of 64, contiguous operands).  An RMSNorm can be folded into the linears around it:
+        ``add_into=(resid, next_w)``: the linear before a norm.  Nothing is returned as y; the product is added into the
+        float32 residual and, with ``next_w`` (the norm's weight; None if no norm follows), the call returns
+        ``(xw, ss)``: the new residual times that weight in bfloat16, and per 16-column tile and row the sum of squares.
+        ``scale_from=(ss, width, eps)``: the linear after the norm, given ``xw`` as x: its rows are scaled by 1 / rms."""
         M, K = x.shape
         N = w.shape[0]
-        y = torch.empty((M, N // 2 if silu_mul else N), dtype=out_dtype or x.dtype, device=x.device)
         self._note_weight(w)
-        self._check(self.lib.linear_stream(_p(x), _p(w), _p(y), _code(y), int(silu_mul), M, N, K, _p(self.status),
-                                           self._stream()), "linear_stream")
+        ss_in, parts, width, eps = (None, 0, 0, 0.0) if scale_from is None else (scale_from[0], scale_from[0].numel() // 16,
+                                                                                 scale_from[1], scale_from[2])
+        if add_into is not None:
+            resid, next_w = add_into
+            xw = torch.empty((M, N), dtype=torch.bfloat16, device=x.device) if next_w is not None else None
+            ss = torch.empty(-(-N // 16) * 16, dtype=torch.float32, device=x.device) if next_w is not None else None
+            self._check(self.lib.linear_stream_norm(_p(x), _p(w), None, DT_BF16, 2, M, N, K, _p(ss_in), parts, width,
+                                                    ctypes.c_float(eps), _p(resid), _p(next_w), _p(xw), _p(ss), _p(self.status),
+                                                    self._stream()), "linear_stream_norm")
+            return xw, ss
+        y = torch.empty((M, N // 2 if silu_mul else N), dtype=out_dtype or x.dtype, device=x.device)
+        self._check(self.lib.linear_stream_norm(_p(x), _p(w), _p(y), _code(y), int(silu_mul), M, N, K, _p(ss_in), parts, width,
+                                                ctypes.c_float(eps), None, None, None, None, _p(self.status), self._stream()),
+                    "linear_stream_norm")
         return y
 
     def _stream_linear(self, M: int, N: int, K: int) -> bool:

@@ -161,13 +161,19 @@ class DecoderModel:
         resid = self.embedding.forward(ctx)
         delta = None
         view_of = lambda k: cache.layer_view(self.run_owner[k], writes=self.runs[k].cache_of is None, state_run=k)  # noqa: E731
-        stacks = self.stacks if (self.stacks and ctx.decode_only and ctx.T == ctx.S and ctx.T <= STACK_MAX_ROWS
-                                 and getattr(self.rt.ops, "fused_layers", False)) else {}
+        # decode steps of few rows: stretches of layers as one launch (off by default), or as a chain of streamed linears
+        # with the norms folded into them
+        stacks = self.stacks if (self.stacks and ctx.decode_only and ctx.T == ctx.S and ctx.T <= STACK_MAX_ROWS) else {}
+        one_launch = getattr(self.rt.ops, "fused_layers", False)
         i = 0
         while i < len(self.runs):
             stack = stacks.get(i)
-            if stack is not None and stack.supports(ctx.T):
+            if stack is not None and one_launch and stack.supports(ctx.T):
                 stack.forward(resid, delta, ctx, [view_of(k) for k in range(stack.first, stack.end)])
+                delta, i = None, stack.end
+                continue
+            if stack is not None and stack.chain_supports(ctx.T):
+                stack.forward_chain(resid, delta, ctx, [view_of(k) for k in range(stack.first, stack.end)])
                 delta, i = None, stack.end
                 continue
             delta = self.blocks[self.runs[i].layer].forward(resid, delta, ctx, view_of(i))

@@ -15,13 +15,20 @@ pytestmark = pytest.mark.gpu
 def _load(model_dir, page):
     from atoma_infer_b200.engine.runtime import load_model
 
-    lm = load_model(model_dir, dtype="bfloat16", page_size=page, num_pages=600, max_seqs=40)
+    lm = load_model(model_dir, dtype="bfloat16", page_size=page, num_pages=900, max_seqs=64)
     return lm
 
 
+MODES = {  # name -> (one launch for all layers, norms folded into streamed linears)
+    "fused": (True, False),
+    "chain": (False, True),
+    "parts": (False, False),
+}
+
+
 def _decode_and_compare(lm, cfg, w, lengths, steps, seed, one_launch=True):
-    """Twin requests: one set decodes through the layer kernel, the other part by part; both against the plain
-    implementation on the whole sequences."""
+    """Triplet requests: one set decodes through the layer kernel, one through the chain of streamed linears with the
+    norms folded in, one part by part; all against the plain implementation on the whole sequences."""
     from atoma_infer_b200.engine import StepEntry
 
     ops, step = lm.rt.ops, lm.step
@@ -29,28 +36,35 @@ def _decode_and_compare(lm, cfg, w, lengths, steps, seed, one_launch=True):
     g = torch.Generator().manual_seed(seed)
     seqs = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
     n = len(seqs)
-    for twin in (0, 1):
+    for k in range(len(MODES)):
         for i, s in enumerate(seqs):
-            step.run([StepEntry(1000 * twin + i, s, [])])
-    worst = {"fused": 0.0, "parts": 0.0}
-    for _ in range(steps):
-        nxt = torch.randint(0, vocab, (n,), generator=g).tolist()
+            step.run([StepEntry(1000 * k + i, s, [])])
+    worst = {name: 0.0 for name in MODES}
+    launches = {}
+    was = ops.fused_layers, ops.fold_norms
+    try:
+        for _ in range(steps):
+            nxt = torch.randint(0, vocab, (n,), generator=g).tolist()
+            for i in range(n):
+                seqs[i].append(nxt[i])
+            ref = torch.stack([P.forward(w, cfg, s, compute=torch.float32)[-1] for s in seqs])
+            for k, (name, (fused, fold)) in enumerate(MODES.items()):
+                ops.fused_layers, ops.fold_norms = fused, fold
+                before = ops.launches
+                got = step.run([StepEntry(1000 * k + i, [nxt[i]], [0]) for i in range(n)]).float().cpu()
+                launches[name] = ops.launches - before
+                ops.check_status()
+                err = ((got - ref).abs().max() / ref.abs().max()).item()
+                worst[name] = max(worst[name], err)
+    finally:
+        ops.fused_layers, ops.fold_norms = was
+    if one_launch:
+        assert launches["fused"] <= 6, "the layers did not run as one launch"
+    for k in range(len(MODES)):
         for i in range(n):
-            seqs[i].append(nxt[i])
-        ref = torch.stack([P.forward(w, cfg, s, compute=torch.float32)[-1] for s in seqs])
-        for name, fused, base in (("fused", True, 0), ("parts", False, 1000)):
-            ops.fused_layers = fused
-            before = ops.launches
-            got = step.run([StepEntry(base + i, [nxt[i]], [0]) for i in range(n)]).float().cpu()
-            if fused and one_launch:
-                assert ops.launches - before <= 6, "the layers did not run as one launch"
-            ops.check_status()
-            err = ((got - ref).abs().max() / ref.abs().max()).item()
-            worst[name] = max(worst[name], err)
-    for i in range(n):
-        step.finish(i)
-        step.finish(1000 + i)
+            step.finish(1000 * k + i)
     assert lm.manager.audit() == ""
+    worst["launches"] = launches
     return worst
 
 
@@ -72,7 +86,10 @@ def test_layer_kernel_against_plain_and_parts(tiny_models, name, page, lengths):
     assert stack.supports(len(lengths)) and stack.end - stack.first == cfg["num_hidden_layers"]
     worst = _decode_and_compare(lm, cfg, helpers.read_weights(d), lengths, steps=5, seed=len(lengths))
     assert worst["fused"] <= helpers.BF16_TOL, worst
+    assert worst["chain"] <= helpers.BF16_TOL, worst
     assert worst["parts"] <= helpers.BF16_TOL, worst
+    if 2 <= len(lengths) <= 8:  # the chain has no norm kernels but the first: fewer launches than part by part
+        assert worst["launches"]["chain"] < worst["launches"]["parts"], worst
 
 
 def test_layer_kernel_refuses_widths_that_are_no_multiple_of_64(tiny_models):
@@ -81,7 +98,7 @@ def test_layer_kernel_refuses_widths_that_are_no_multiple_of_64(tiny_models):
     assert all(not s.supports(4) for s in lm.model.stacks.values())
     lm.rt.ops.fused_layers = True
     worst = _decode_and_compare(lm, cfg, helpers.read_weights(d), [5, 9, 30], steps=2, seed=1, one_launch=False)  # runs part by part
-    assert max(worst.values()) <= helpers.BF16_TOL
+    assert max(worst[k] for k in MODES) <= helpers.BF16_TOL
 
 
 def test_layer_kernel_in_captured_graphs_generates_what_the_plain_model_would(tiny_models):
