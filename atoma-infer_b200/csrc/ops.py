@@ -90,6 +90,7 @@ class CudaOps:
         # (see _stream_linear); ATOMA_INFER_STREAM_LINEAR=0 keeps them all on the kernel that loads weights into
         # fragments directly (kernels/linear_bf16.cu).  The kernel tests set the attribute.
         self.stream_linear = os.environ.get("ATOMA_INFER_STREAM_LINEAR", "1") != "0"
+        self.stream_min_rows = int(os.environ.get("ATOMA_INFER_STREAM_MIN_ROWS", "1"))  # a test and measurement lever
         # In decode steps whose linears are streamed, the RMSNorms between them are folded into them (parts/decode_stack.py,
         # the chain); ATOMA_INFER_FOLD_NORMS=0 leaves the norm a kernel of its own.
         self.fold_norms = os.environ.get("ATOMA_INFER_FOLD_NORMS", "1") != "0"
@@ -256,17 +257,19 @@ class CudaOps:
         return y
 
     def _stream_linear(self, M: int, N: int, K: int) -> bool:
-        """Whether a bfloat16 linear of M <= 16 rows runs on the TMA-fed persistent kernel.  Measured, decode step as a
-        CUDA graph, direct against streamed: Llama 3.2 1B sizes, batch 1 / 2 / 4 / 8 / 12 / 16: 0.758 / 0.800 / 0.831 /
-        0.878 / 1.125 / 1.265 ms against 0.778 / 0.791 / 0.805 / 0.829 / 0.918 / 0.944; 8 layers of the 3B sizes, batch
-        1 / 8: 0.539 / 0.656 against 0.559 / 0.646; of the 8B sizes: 0.918 / 1.040 against 0.814 / 0.912.  So: two rows
-        and more always (the direct kernel is a quarter to a third slower with two n-tiles, 9 to 16 rows); a single row
-        only where every matrix is large (both sides at least 4,096), since a persistent kernel holds the whole GPU and
-        the kernel after it cannot start early.  Mixing the two within a layer is the slowest choice (3B sizes, batch 8:
-        all direct 0.656 ms, all streamed 0.641, streamed only where its tiles fill the blocks evenly 0.733 to 0.751)."""
+        """Whether a bfloat16 linear of M <= 16 rows runs on the TMA-fed persistent kernel: whenever it can (K a multiple
+        of 64).  Measured, decode step as a CUDA graph, all linears direct against all streamed: Llama 3.2 1B sizes, batch
+        1 / 2 / 4 / 8 / 12 / 16: 0.758 / 0.800 / 0.831 / 0.878 / 1.125 / 1.265 ms against 0.778 / 0.791 / 0.805 / 0.829 /
+        0.918 / 0.944, and with the norms folded into the streamed linears (up to 8 rows) 0.746 / 0.763 / - / 0.826;
+        8 layers of the 3B sizes, batch 1 / 8: 0.539 / 0.656 against 0.535 (folded) / 0.641; of the 8B sizes: 0.918 / 1.040
+        against 0.802 / 0.912.  The direct kernel is a quarter to a third slower with two n-tiles (9 to 16 rows).  Mixing
+        the two within a layer is the slowest choice (3B sizes, batch 8: streamed only where its tiles fill the blocks
+        evenly 0.733 to 0.751 ms; 1B sizes, batch 1, gate/up alone streamed 0.837): a persistent kernel holds every
+        multiprocessor's shared memory until its blocks leave, so a kernel of another kind after it cannot start early.
+        ``stream_min_rows`` (ATOMA_INFER_STREAM_MIN_ROWS) keeps steps of fewer rows on the direct kernel."""
         if not self.stream_linear or M > SKINNY_MAX_ROWS or K % 64:
             return False
-        return M >= 2 or min(N, K) >= 4096
+        return M >= self.stream_min_rows
 
     def _swiglu_on_tcgen05(self, M: int, n_out: int, K: int) -> bool:
         """Whether the gate/up product with the SwiGLU epilogue runs on the persistent tcgen05 kernel instead
