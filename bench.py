@@ -8,6 +8,10 @@ K steps, timed on the device; ``e2e`` is the same through ``Engine.step()``, wit
 step's inputs copied from pinned host memory and the sampled tokens read back every
 step.  Also: prefill of 2,048 tokens, decode at batch 1 and 64, and the decode step's
 fraction of the measured HBM bandwidth.  Prints ONE JSON line.
+
+Tables for profiles/ instead of the JSON line: ``--linears [--model 1b|3b|8b]`` (the two few-row linear
+kernels on the four matrices of a layer) and ``--layer-kernel-phases`` (the persistent layer kernel's time
+per phase); ``--model 3b|8b`` alone runs that configuration's serving workload through ``Engine.generate``.
 """
 from __future__ import annotations
 
