@@ -565,10 +565,14 @@ extern "C" int silu_mul(const void* gu, void* out, int dtype, const int* meta, i
 }
 
 // ----------------------------------------------------------------------------- weights ahead of time
-// A kernel of its own that only asks byte ranges into L2 (see PrefetchRanges) and ends at once.
+// A kernel of its own that only asks byte ranges into L2 (see PrefetchRanges).  It reads and writes nothing of
+// the step, yet it waits for the kernel before it like every other one: a dependent launch waits only for the
+// grid directly ahead of it, so a link of the chain that ended early would let the kernel behind it (the
+// attention) run ahead of the projection whose rows it reads.
 __global__ void l2_prefetch_kernel(const PrefetchRanges r) {
     pdl_launch_dependents();
     prefetch_ranges_l2(r, (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x, (unsigned long long)gridDim.x * blockDim.x);
+    pdl_wait();
 }
 extern "C" int l2_prefetch(int n, const void* const* ptrs, const unsigned long long* bytes, cudaStream_t stream) {
     const PrefetchRanges r = make_prefetch_ranges(n, ptrs, bytes);
