@@ -14,7 +14,9 @@
 // is a third full.  Cutting a tile's k range into 2 to 8 parts that different blocks take (partial sums to scratch, the
 // last part to arrive adds them up) was measured and is not kept: the fence, the atomic and the read of the partial
 // sums cost each part 2 to 3 us, more than the idle blocks (q/k/v of Llama 3.2 1B at 8 rows: 3.7 -> 9.7 us; down:
-// 7.7 -> 22.4 us).
+// 7.7 -> 22.4 us).  Also measured and not kept: blocks of half the shared memory (a ring of 4 or 5 stages), so that
+// the blocks of the next streamed linear find room beside them and fill their rings while these drain: the decode
+// step of Llama 3.2 1B at 8 rows 0.826 -> 0.926 ms; sixteen arithmetic warps instead of eight: 0.840 ms.
 //
 // Against the few-row linear that loads weights with 16-byte loads straight into fragments (linear_bf16.cu) this one
 // keeps more bytes in flight per multiprocessor with one instruction per 16 KB and keeps two n-tiles (9 to 16 rows) as

@@ -474,7 +474,8 @@ def main() -> int:
     clock_rec = clocks.stop()
 
     rec = {
-        "metric": "decode tok/s (Llama 3.2 1B, batch 8, 2,048-token prompts)", "value": roofline["tok_s"], "unit": "tok/s",
+        "metric": f"decode tok/s (Llama 3.2 1B, batch {args.batch}, {prompt_len:,}-token prompts)", "value": roofline["tok_s"],
+        "unit": "tok/s",
         "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": roofline["ms_per_step"],
         "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
