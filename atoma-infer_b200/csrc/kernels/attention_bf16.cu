@@ -72,14 +72,18 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap map_kv, int use_tma, bf16
         for (int w = 0; w < DEC_WARPS; ++w) { mbar_init(&tile_bar[w][0], 1); mbar_init(&tile_bar[w][1], 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    const bool live = e < meta[META_NUM_ENTRIES];
+    // Every entry of a decode step brings one token, so entry e is row e; what the block needs of the step's
+    // metadata is fetched in one round of independent loads (the block table is the second, the keys the third).
+    const int num_entries = meta[META_NUM_ENTRIES], newest = positions[e];
+    const int bt_offset = meta[META_BT_OFFSET + group], bt_stride = meta[META_BT_STRIDE + group];
+    const bool live = e < num_entries;
     const int G = nq / L.num_kv_heads;
-    const int row0 = live ? cu_tokens[e] : 0;
-    const int kv_len = live ? positions[row0] + 1 : 0;
+    const int row0 = e;
+    const int kv_len = live ? newest + 1 : 0;
     const int kstart = window > 0 ? max(0, kv_len - window) : 0;
     const int per = (((kv_len - kstart + splits - 1) / splits + DEC_KT - 1) / DEC_KT) * DEC_KT;
     const int lo = kstart + split * per, hi = min(kv_len, lo + per);
-    const int* bt = meta + meta[META_BT_OFFSET + group] + (size_t)e * meta[META_BT_STRIDE + group];
+    const int* bt = meta + bt_offset + (size_t)e * bt_stride;
     // A lane copies the same rows of every tile; the pages of a tile's rows are fetched from the block
     // table into registers one tile ahead, so no copy waits for a table lookup.
     constexpr int PAIRS = D / 16, RPL = DEC_KT * PAIRS / 32;  // 32-byte sectors per row; rows*sectors per lane
