@@ -579,6 +579,12 @@ extern "C" int l2_prefetch(int n, const void* const* ptrs, const unsigned long l
     if (!(r.bytes[0] | r.bytes[1] | r.bytes[2] | r.bytes[3])) return 0;
     return (int)launch_kernel(l2_prefetch_kernel, 64, 128, 0, stream, r);
 }
+// The same on a stream of its own, beside the step's chain of dependent launches: an ordinary launch.
+extern "C" int l2_prefetch_aside(int n, const void* const* ptrs, const unsigned long long* bytes, cudaStream_t stream) {
+    const PrefetchRanges r = make_prefetch_ranges(n, ptrs, bytes);
+    if (!(r.bytes[0] | r.bytes[1] | r.bytes[2] | r.bytes[3])) return 0;
+    return (int)launch_kernel_pdl(false, l2_prefetch_kernel, 64, 128, 0, stream, r);
+}
 
 // ----------------------------------------------------------------------------- casts
 template <typename TI, typename TO>

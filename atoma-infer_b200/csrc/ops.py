@@ -102,6 +102,9 @@ class CudaOps:
         # at most this many bytes (0: never); see _prefetch_next_weight.
         self.prefetch_bytes = int(float(os.environ.get("ATOMA_INFER_PREFETCH_MB", "12")) * (1 << 20))
         self._order, self._order_index, self._starts, self._cursor = [], {}, [], 0
+        # ... on a stream of its own when the step has at most this many rows, else as a link of the step's chain
+        self.prefetch_aside_rows = int(os.environ.get("ATOMA_INFER_PREFETCH_ASIDE_ROWS", "4"))
+        self._side_stream, self._side_pending = None, False
         self.lib.kernels_set_pdl(int(self.pdl))
         self.num_sms = torch.cuda.get_device_properties(self.device).multi_processor_count
 
@@ -164,19 +167,45 @@ class CudaOps:
         if where:
             self._cursor = next((k for k in where if k >= self._cursor), where[0]) + 1
 
-    def _prefetch_next_weight(self) -> None:
+    def _prefetch_next_weight(self, rows: int = 0) -> None:
         """Before the decode attention of a small batch: asks the weight of the linear after it (the next one in the
         stream after the last linear that ran) into L2, if it is a small one (``prefetch_bytes`` at most).  A small
         matrix is read in a few microseconds that are mostly start-up and drain; read from L2 it is shorter, and the
         attention of a small batch leaves the bandwidth to bring it there.  Measured, decode step at batch 8: Llama
         3.2 1B (8.4 MB) 0.924 -> 0.897 ms; asking for more than that one weight, or from inside the linears, is
-        slower; at the 3B and 8B sizes (18.9 and 33.5 MB) asking at all is 3 to 5 % slower, hence the limit."""
+        slower; at the 3B and 8B sizes (18.9 and 33.5 MB) asking at all is 3 to 5 % slower, hence the limit.
+        ``rows``: the step's rows.  With at most ``prefetch_aside_rows`` of them (ATOMA_INFER_PREFETCH_ASIDE_ROWS) the
+        request runs on a stream of its own beside the step's chain; measured in the chain against beside it, decode
+        step of Llama 3.2 1B: batch 1 0.744 / 0.730 ms, batch 2 0.763 / 0.744, batch 4 0.773 / 0.745, batch 8 0.820 /
+        0.839."""
         if self._cursor >= len(self._order):
             return
         ptr, size = self._order[self._cursor]
-        if size <= self.prefetch_bytes:
+        if size > self.prefetch_bytes:
+            return
+        if rows > self.prefetch_aside_rows:
             self._check(self.lib.l2_prefetch(1, (ctypes.c_void_p * 1)(ptr), (ctypes.c_ulonglong * 1)(size), self._stream()),
                         "l2_prefetch")
+            return
+        # on a stream of its own, after what the step has launched so far: the attention then follows the projection
+        # directly in the chain of dependent launches
+        main = torch.cuda.current_stream(self.device)
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream(self.device)
+        fork = torch.cuda.Event()
+        fork.record(main)
+        self._side_stream.wait_event(fork)
+        self._check(self.lib.l2_prefetch_aside(1, (ctypes.c_void_p * 1)(ptr), (ctypes.c_ulonglong * 1)(size),
+                                               ctypes.c_void_p(self._side_stream.cuda_stream)), "l2_prefetch")
+        self._side_pending = True
+
+    def join_side_work(self) -> None:
+        """What ran beside the step's stream (see _prefetch_next_weight) joins it: called at the end of a forward pass."""
+        if self._side_pending:
+            done = torch.cuda.Event()
+            done.record(self._side_stream)
+            torch.cuda.current_stream(self.device).wait_event(done)
+            self._side_pending = False
 
     # ------------------------------------------------------------------ kernels
     def embed(self, tokens, table, resid, meta, T: int, scale: float = 1.0):
@@ -348,7 +377,7 @@ class CudaOps:
                 splits = self.decode_splits(S, nkv, ctx.max_context, lib.attn_decode_blocks_per_sm())
                 # the splits merge inside a thread-block cluster when they fit one, else through scratch
                 if S <= SKINNY_MAX_ROWS:
-                    self._prefetch_next_weight()
+                    self._prefetch_next_weight(S)
                 cluster = self.decode_cluster and 1 < splits <= lib.attn_decode_max_cluster()
                 n = 0 if cluster else lib.attn_decode_scratch_floats(S, nq, splits)
                 scratch = torch.empty(n, dtype=torch.float32, device=q.device) if n else None

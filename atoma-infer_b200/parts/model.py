@@ -179,6 +179,13 @@ class DecoderModel:
             delta = self.blocks[self.runs[i].layer].forward(resid, delta, ctx, view_of(i))
             i += 1
         if num_rows == 0:
+            join = getattr(self.rt.ops, "join_side_work", None)
+            if join is not None:
+                join()
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.rt.device)
         h = self.final_norm.forward(resid, delta, ctx, rows=rows, num_rows=num_rows)
-        return self.head.forward(h, ctx)
+        logits = self.head.forward(h, ctx)
+        join = getattr(self.rt.ops, "join_side_work", None)
+        if join is not None:
+            join()
+        return logits
